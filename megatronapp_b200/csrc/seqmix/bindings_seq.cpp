@@ -70,8 +70,8 @@ void gated_head_rms_norm(const Tensor& o, const Tensor& w, c10::optional<Tensor>
   count(); check_last_error("gated_head_rms_norm");
 }
 
-void causal_conv(const Tensor& x, const Tensor& w, const Tensor& cu, const Tensor& rows, const Tensor& tok_seq, Tensor window,
-                 Tensor y, int64_t max_len, bool silu) {
+void causal_conv(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, const Tensor& cu, const Tensor& rows,
+                 const Tensor& tok_seq, Tensor window, Tensor y, int64_t max_len, bool silu) {
   const bool bf16 = act_is_bf16(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "x must be [T, C] with unit inner stride");
   const int T = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1)), taps = static_cast<int>(w.size(1));
@@ -81,8 +81,13 @@ void causal_conv(const Tensor& x, const Tensor& w, const Tensor& cu, const Tenso
               window.size(2) == C, "window must be [rows, taps - 1, C]");
   check_i32(cu, "cu"); check_i32(rows, "rows"); check_i32(tok_seq, "tok_seq");
   TORCH_CHECK(tok_seq.numel() == T && cu.numel() == rows.numel() + 1, "bad packed-batch tensors");
+  const void* bp = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->scalar_type() == x.scalar_type() && bias->is_contiguous() && bias->numel() == C, "bad conv bias");
+    bp = bias->data_ptr();
+  }
   c10::cuda::CUDAGuard g(x.device());
-  b200seq::causal_conv_silu(x.data_ptr(), x.stride(0), w.data_ptr(), cu.data_ptr<int>(), rows.data_ptr<int>(), tok_seq.data_ptr<int>(),
+  b200seq::causal_conv_silu(x.data_ptr(), x.stride(0), w.data_ptr(), bp, cu.data_ptr<int>(), rows.data_ptr<int>(), tok_seq.data_ptr<int>(),
                             window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), silu, bf16,
                             cur_stream());
   count(2); check_last_error("causal_conv_silu");
@@ -348,12 +353,160 @@ void clamped_glu(const Tensor& x, Tensor y, double limit, double alpha, double s
   count(); check_last_error("clamped_glu");
 }
 
+
+
+void stream_mix_norm(Tensor x, c10::optional<Tensor> a, c10::optional<Tensor> b, c10::optional<Tensor> bias_a, c10::optional<Tensor> ls,
+                     double scale_a, double scale_b, c10::optional<Tensor> mix, c10::optional<Tensor> outc, c10::optional<Tensor> inp,
+                     c10::optional<Tensor> w, c10::optional<Tensor> beta, c10::optional<Tensor> h, double eps, bool center) {
+  check_f32(x, "x");
+  TORCH_CHECK(x.dim() == 3, "x must be [T, S, W]");
+  b200seq::StreamNormArgs p{};
+  p.x = x.data_ptr<float>(); p.S = static_cast<int>(x.size(1)); p.W = static_cast<int>(x.size(2));
+  const int64_t T = x.size(0);
+  bool bf16 = false, have_dtype = false;
+  auto act = [&](const Tensor& t, const char* name) {
+    const bool is = act_is_bf16(t, name);
+    TORCH_CHECK(!have_dtype || is == bf16, name, ": activation dtypes differ");
+    bf16 = is; have_dtype = true;
+  };
+  auto vec = [&](const c10::optional<Tensor>& t, const char* name) -> const void* {
+    if (!(t.has_value() && t->defined())) return nullptr;
+    act(*t, name);
+    TORCH_CHECK(t->is_contiguous() && t->numel() == p.W, name, " must hold W values");
+    return t->data_ptr();
+  };
+  auto rows2 = [&](const c10::optional<Tensor>& t, const char* name, int64_t& ld) -> const void* {
+    if (!(t.has_value() && t->defined())) return nullptr;
+    act(*t, name);
+    TORCH_CHECK(t->dim() == 2 && t->size(0) == T && t->size(1) == p.W && t->stride(1) == 1, name, " must be [T, W] with unit inner stride");
+    ld = t->stride(0);
+    return t->data_ptr();
+  };
+  p.a = rows2(a, "a", p.lda); p.b = rows2(b, "b", p.ldb);
+  p.bias_a = vec(bias_a, "bias_a"); p.ls = vec(ls, "ls");
+  p.scale_a = static_cast<float>(scale_a); p.scale_b = static_cast<float>(scale_b);
+  if (p.a != nullptr) {
+    TORCH_CHECK(mix.has_value() && outc.has_value(), "an update needs mix and out coefficients");
+    check_f32(*mix, "mix"); check_f32(*outc, "outc");
+    TORCH_CHECK(mix->numel() == p.S * p.S && outc->numel() == p.S, "mix must be [S, S], outc [S]");
+    p.mix = mix->data_ptr<float>(); p.outc = outc->data_ptr<float>();
+  }
+  if (inp.has_value() && inp->defined()) {
+    check_f32(*inp, "inp");
+    TORCH_CHECK(inp->numel() == p.S && w.has_value() && h.has_value(), "inp must be [S]; the norm needs w and h");
+    p.inp = inp->data_ptr<float>();
+    p.w = vec(w, "w"); p.beta = vec(beta, "beta");
+    act(*h, "h");
+    TORCH_CHECK(h->is_contiguous() && h->numel() == T * p.W, "h must be contiguous [T, W]");
+    p.h = h->data_ptr();
+  }
+  p.eps = static_cast<float>(eps); p.center = center ? 1 : 0;
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(b200seq::stream_mix_norm(p, static_cast<int>(T), bf16, cur_stream()), "stream_mix_norm: ", p.S, " streams of width ", p.W,
+              " have no kernel instance");
+  count(); check_last_error("stream_mix_norm");
+}
+
+void add_sinusoid(Tensor x, const Tensor& positions, const Tensor& freq) {
+  check_f32(x, "x"); check_f32(freq, "freq");
+  TORCH_CHECK(x.dim() == 2 && x.size(1) % 2 == 0 && freq.numel() == x.size(1) / 2, "x must be [T, W] with even W and W / 2 frequencies");
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() == x.size(0),
+              "positions must be a contiguous int64 CUDA tensor [T]");
+  c10::cuda::CUDAGuard g(x.device());
+  b200seq::add_sinusoid(x.data_ptr<float>(), positions.data_ptr<int64_t>(), freq.data_ptr<float>(), static_cast<int>(x.size(0)),
+                        static_cast<int>(x.size(1)), cur_stream());
+  count(); check_last_error("add_sinusoid");
+}
+
+void head_rms_norm(const Tensor& x, const Tensor& w, Tensor y, double eps) {
+  const bool bf16 = act_is_bf16(x, "x");
+  check_rows(x, "x");
+  TORCH_CHECK(w.scalar_type() == x.scalar_type() && w.is_contiguous() && w.numel() == x.size(2), "weight must hold one value per channel of a head");
+  TORCH_CHECK(y.scalar_type() == x.scalar_type() && y.is_contiguous() && y.numel() == x.numel(), "bad y");
+  c10::cuda::CUDAGuard g(x.device());
+  b200seq::head_rms_norm(x.data_ptr(), x.stride(0), w.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                         static_cast<int>(x.size(2)), static_cast<float>(eps), bf16, cur_stream());
+  count(); check_last_error("head_rms_norm");
+}
+
+void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const Tensor& block_table, const Tensor& tok_req,
+                            const Tensor& tok_len, c10::optional<Tensor> slopes, c10::optional<Tensor> gate, Tensor out, int64_t block_size,
+                            double scale, int64_t window, bool sink, double out_scale) {
+  const bool bf16 = act_is_bf16(q, "q");
+  check_rows(q, "q");
+  TORCH_CHECK(kcache.scalar_type() == q.scalar_type() && vcache.scalar_type() == q.scalar_type() && kcache.dim() == 3 && vcache.dim() == 3 &&
+              kcache.is_contiguous() && vcache.is_contiguous() && kcache.size(2) == q.size(2) && vcache.size(1) == kcache.size(1),
+              "caches must be contiguous [slots, G, d] / [slots, G, dv] in q's dtype");
+  check_i32(block_table, "block_table"); check_i32(tok_req, "tok_req"); check_i32(tok_len, "tok_len");
+  b200seq::WindowAttnArgs p{};
+  p.n_tok = static_cast<int>(q.size(0));
+  p.H = static_cast<int>(q.size(1)); p.G = static_cast<int>(kcache.size(1)); p.d = static_cast<int>(q.size(2));
+  p.dv = static_cast<int>(vcache.size(2));
+  TORCH_CHECK(block_table.dim() == 2 && tok_req.numel() == q.size(0) && tok_len.numel() == q.size(0), "bad packed-batch tensors");
+  TORCH_CHECK(out.scalar_type() == q.scalar_type() && out.is_contiguous() && out.numel() == q.size(0) * p.H * p.dv, "bad out");
+  p.q = q.data_ptr(); p.ldq = q.stride(0); p.kcache = kcache.data_ptr(); p.vcache = vcache.data_ptr();
+  p.block_table = block_table.data_ptr<int>(); p.tok_req = tok_req.data_ptr<int>(); p.tok_len = tok_len.data_ptr<int>();
+  if (slopes.has_value() && slopes->defined()) {
+    check_f32(*slopes, "slopes");
+    TORCH_CHECK(slopes->numel() == p.H, "slopes must be [H]");
+    p.slopes = slopes->data_ptr<float>();
+  }
+  if (gate.has_value() && gate->defined()) {
+    check_act2(*gate, q, "gate");
+    TORCH_CHECK(gate->size(0) == q.size(0) && gate->size(1) == p.H, "gate must be [T, H]");
+    p.gate = gate->data_ptr(); p.ldg = gate->stride(0);
+  }
+  p.out = out.data_ptr();
+  p.block_size = static_cast<int>(block_size); p.max_blocks = static_cast<int>(block_table.size(1));
+  p.scale = static_cast<float>(scale); p.out_scale = static_cast<float>(out_scale);
+  p.window = static_cast<int>(window); p.sink = sink ? 1 : 0;
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(b200seq::window_attention_paged(p, bf16, cur_stream()), "window_attention_paged: no kernel instance for heads ", p.H, " / ",
+              p.G, ", dims ", p.d, " / ", p.dv);
+  count(); check_last_error("window_attention_paged");
+}
+
+void selective_scan(const Tensor& x, c10::optional<Tensor> z, const Tensor& B, const Tensor& Cm, const Tensor& dt_pre,
+                    c10::optional<Tensor> dt_bias, const Tensor& A_log, const Tensor& D, const Tensor& cu, const Tensor& rows, Tensor state,
+                    Tensor y, double out_scale) {
+  const bool bf16 = act_is_bf16(x, "x");
+  check_act2(x, x, "x"); check_act2(B, x, "B"); check_act2(Cm, x, "C"); check_act2(y, x, "y");
+  check_f32(state, "state"); check_i32(cu, "cu"); check_i32(rows, "rows");
+  b200seq::SelScanArgs p{};
+  p.C = static_cast<int>(x.size(1)); p.N = static_cast<int>(B.size(1));
+  const int64_t T = x.size(0);
+  TORCH_CHECK(B.size(0) == T && Cm.size(0) == T && Cm.size(1) == p.N && y.size(0) == T && y.size(1) == p.C, "bad B / C / y shapes");
+  TORCH_CHECK(dt_pre.is_cuda() && dt_pre.scalar_type() == at::kFloat && dt_pre.dim() == 2 && dt_pre.stride(1) == 1 && dt_pre.size(0) == T &&
+              dt_pre.size(1) == p.C, "dt_pre must be fp32 [T, C]");
+  TORCH_CHECK(state.dim() == 3 && state.size(1) == p.C && state.size(2) == p.N, "state must be [rows, C, N]");
+  TORCH_CHECK(A_log.scalar_type() == x.scalar_type() && A_log.is_contiguous() && A_log.numel() == static_cast<int64_t>(p.C) * p.N &&
+              D.scalar_type() == x.scalar_type() && D.is_contiguous() && D.numel() == p.C, "bad A_log / D");
+  if (z.has_value() && z->defined()) { check_act2(*z, x, "z"); TORCH_CHECK(z->size(0) == T && z->size(1) == p.C, "bad z"); p.z = z->data_ptr(); p.ldz = z->stride(0); }
+  if (dt_bias.has_value() && dt_bias->defined()) {
+    TORCH_CHECK(dt_bias->scalar_type() == x.scalar_type() && dt_bias->is_contiguous() && dt_bias->numel() == p.C, "bad dt_bias");
+    p.dt_bias = dt_bias->data_ptr();
+  }
+  p.x = x.data_ptr(); p.B = B.data_ptr(); p.Cm = Cm.data_ptr(); p.y = y.data_ptr(); p.dt_pre = dt_pre.data_ptr<float>();
+  p.ldx = x.stride(0); p.ldb = B.stride(0); p.ldc = Cm.stride(0); p.ldy = y.stride(0); p.lddt = dt_pre.stride(0);
+  p.A_log = A_log.data_ptr(); p.D = D.data_ptr();
+  p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>(); p.state = state.data_ptr<float>();
+  p.out_scale = static_cast<float>(out_scale);
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(b200seq::selective_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "selective_scan: ", p.N,
+              " states per channel exceed the largest kernel instance (128)");
+  count(); check_last_error("selective_scan");
+}
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rms_norm", &add_rms_norm);
   m.def("gated_head_rms_norm", &gated_head_rms_norm);
   m.def("causal_conv", &causal_conv);
+  m.def("stream_mix_norm", &stream_mix_norm);
+  m.def("add_sinusoid", &add_sinusoid);
+  m.def("head_rms_norm", &head_rms_norm);
+  m.def("window_attention_paged", &window_attention_paged);
+  m.def("selective_scan", &selective_scan);
   m.def("delta_rule_scan", &delta_rule_scan);
   m.def("mlstm_scan", &mlstm_scan);
   m.def("latent_attention_paged", &latent_attention_paged);

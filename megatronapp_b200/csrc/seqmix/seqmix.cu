@@ -70,7 +70,8 @@ __global__ void gated_head_rms_norm_kernel(const float* __restrict__ o, const T*
 // depth-wise causal convolution (+ SiLU when asked for); the window holds the taps - 1 inputs that preceded the step
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, const int* __restrict__ cu,
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, const T* __restrict__ bias,
+                                        const int* __restrict__ cu,
                                         const int* __restrict__ rows, const int* __restrict__ tok_seq, const T* __restrict__ window,
                                         T* __restrict__ y, int n_tok, int C, int taps, int silu) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -78,7 +79,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, co
   const int t = static_cast<int>(idx / C), c = static_cast<int>(idx % C);
   const int r = tok_seq[t], a = cu[r];
   const T* win = window + static_cast<int64_t>(rows[r]) * (taps - 1) * C;
-  float acc = 0.f;
+  float acc = bias != nullptr ? ld(bias + c) : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int src = t - (taps - 1 - j);
     const float in = src >= a ? ld(x + src * ldx + c) : ld(win + static_cast<int64_t>(taps - 1 + (src - a)) * C + c);
@@ -107,7 +108,7 @@ template <> struct Pair<__nv_bfloat16> {
 
 template <typename T, int TAPS>
 __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w,
-                                                                   const int* __restrict__ cu, const int* __restrict__ rows,
+                                                                   const T* __restrict__ bias, const int* __restrict__ cu, const int* __restrict__ rows,
                                                                    const T* __restrict__ window, T* __restrict__ y, int C, int silu) {
   const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x), r = blockIdx.z;
   const int a = cu[r], b = cu[r + 1];
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __re
   if (c >= C || t_lo >= t_hi) return;
   const T* win = window + static_cast<int64_t>(rows[r]) * (TAPS - 1) * C;
   float2 wt[TAPS], hist[TAPS];
+  const float2 bs = bias != nullptr ? make_float2(ld(bias + c), ld(bias + c + 1)) : make_float2(0.f, 0.f);
 #pragma unroll
   for (int j = 0; j < TAPS; ++j) wt[j] = make_float2(ld(w + static_cast<int64_t>(c) * TAPS + j), ld(w + static_cast<int64_t>(c + 1) * TAPS + j));
 #pragma unroll
@@ -124,7 +126,7 @@ __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __re
   }
   for (int t = t_lo; t < t_hi; ++t) {
     hist[TAPS - 1] = Pair<T>::load(x + t * ldx + c);
-    float2 acc = make_float2(0.f, 0.f);
+    float2 acc = bs;
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) { acc.x = fmaf(wt[j].x, hist[j].x, acc.x); acc.y = fmaf(wt[j].y, hist[j].y, acc.y); }
     if (silu) acc = make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y));
@@ -685,14 +687,17 @@ void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* 
 }
 
 template <typename T, int TAPS>
-static void launch_conv_run(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const void* window, void* y,
+static void launch_conv_run(const void* x, int64_t ldx, const void* w, const void* bias, const int* cu, const int* rows,
+                            const void* window, void* y,
                             int R, int C, int max_len, int silu, cudaStream_t s) {
   dim3 grid((C / 2 + 127) / 128, (max_len + kConvRun - 1) / kConvRun, R);
-  causal_conv_silu_run_kernel<T, TAPS><<<grid, 128, 0, s>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows,
+  causal_conv_silu_run_kernel<T, TAPS><<<grid, 128, 0, s>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(w),
+                                                            static_cast<const T*>(bias), cu, rows,
                                                             static_cast<const T*>(window), static_cast<T*>(y), C, silu);
 }
 
-void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
+void causal_conv_silu(const void* x, int64_t ldx, const void* w, const void* bias, const int* cu, const int* rows, const int* tok_seq,
+                      void* window,
                       void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s) {
   if (n_tok == 0) return;
   const int act = silu ? 1 : 0;
@@ -703,11 +708,12 @@ void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, 
                       reinterpret_cast<uintptr_t>(y) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(window) % pair_bytes == 0 &&
                       max_len > 0 && (max_len + kConvRun - 1) / kConvRun <= 65535 && R <= 65535;
   SEQ_DISPATCH_T(bf16, {
-    if (paired && taps == 2) launch_conv_run<T, 2>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
-    else if (paired && taps == 3) launch_conv_run<T, 3>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
-    else if (paired && taps == 4) launch_conv_run<T, 4>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
+    if (paired && taps == 2) launch_conv_run<T, 2>(x, ldx, w, bias, cu, rows, window, y, R, C, max_len, act, s);
+    else if (paired && taps == 3) launch_conv_run<T, 3>(x, ldx, w, bias, cu, rows, window, y, R, C, max_len, act, s);
+    else if (paired && taps == 4) launch_conv_run<T, 4>(x, ldx, w, bias, cu, rows, window, y, R, C, max_len, act, s);
     else causal_conv_silu_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
-        static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows, tok_seq, static_cast<const T*>(window),
+        static_cast<const T*>(x), ldx, static_cast<const T*>(w), static_cast<const T*>(bias), cu, rows, tok_seq,
+        static_cast<const T*>(window),
         static_cast<T*>(y), n_tok, C, taps, act);
     if (taps > 1)
       conv_window_update_kernel<T><<<(R * C + 255) / 256, 256, 0, s>>>(static_cast<const T*>(x), ldx, cu, rows,

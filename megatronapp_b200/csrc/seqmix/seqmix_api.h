@@ -45,7 +45,7 @@ struct LatentAttnArgs {
 void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, float w_off, bool bf16, cudaStream_t s);
 void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
                          float eps, bool bf16, cudaStream_t s);
-void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
+void causal_conv_silu(const void* x, int64_t ldx, const void* w, const void* bias, const int* cu, const int* rows, const int* tok_seq, void* window,
                       void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s);
 bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s);
 bool mlstm_scan(const MlstmArgs& p, int R, bool bf16, cudaStream_t s);
@@ -117,5 +117,55 @@ int mingru_runs(int max_len);
 void mingru_scan(const MinGruArgs& p, int R, bool bf16, cudaStream_t s);
 void clamped_glu(const void* x, int64_t ldx, void* y, int64_t n_tok, int F, float limit, float alpha, float shift, bool bf16,
                  cudaStream_t s);
+
+struct StreamNormArgs {
+  float* x;                       // [T, S, W] residual streams, updated in place
+  const void *a, *b;              // pending sublayer output(s) [T, W] with row strides lda / ldb (a nullptr: no update)
+  int64_t lda, ldb;
+  const void* bias_a;             // [W] added to a (nullptr: none)
+  const void* ls;                 // [W] layer scale (nullptr: none)
+  float scale_a, scale_b;
+  const float *mix, *outc;        // [S, S] (from, to) and [S]
+  const float* inp;               // [S] read weights of the norm's input (nullptr: no norm, only the update)
+  const void *w, *beta;           // norm weight and bias (beta nullptr: none)
+  void* h;                        // [T, W] normed output
+  int S, W, center;               // center 0: RMS norm
+  float eps;
+};
+
+struct WindowAttnArgs {
+  const void* q;                  // [T, H, d], row stride ldq
+  int64_t ldq;
+  const void *kcache, *vcache;    // [slots, G, d], [slots, G, dv]
+  const int *block_table, *tok_req, *tok_len;
+  const float* slopes;            // [H] distance penalty per head (nullptr: none)
+  const void* gate;               // [T, H] pre-activation of the per-head output gate, row stride ldg (nullptr: none)
+  int64_t ldg;
+  void* out;                      // [T, H * dv]
+  int n_tok, H, G, d, dv, block_size, max_blocks;
+  int window;                     // 0: every earlier key is visible
+  int sink;                       // 1: one is added to the softmax denominator
+  int QB, HC;                     // filled by the launcher
+  float scale, out_scale;
+};
+
+struct SelScanArgs {
+  const void *x, *z, *B, *Cm;     // [T, C], [T, C] (nullptr: no gate), [T, N], [T, N] with row strides
+  int64_t ldx, ldz, ldb, ldc, lddt, ldy;
+  const float* dt_pre;            // [T, C] step size before bias and softplus
+  const void *dt_bias, *A_log, *D;  // [C] (nullptr: none), [C, N], [C]
+  const int *cu, *rows;
+  float* state;                   // [rows, C, N]
+  void* y;                        // [T, C]
+  int C, N;
+  float out_scale;
+};
+
+bool stream_mix_norm(const StreamNormArgs& p, int n_tok, bool bf16, cudaStream_t s);
+void add_sinusoid(float* x, const int64_t* positions, const float* freq, int n_tok, int width, cudaStream_t s);
+void head_rms_norm(const void* x, int64_t ldx, const void* w, void* y, int n_tok, int heads, int d, float eps, bool bf16,
+                   cudaStream_t s);
+bool window_attention_paged(const WindowAttnArgs& p, bool bf16, cudaStream_t s);
+bool selective_scan(const SelScanArgs& p, int R, bool bf16, cudaStream_t s);
 
 }  // namespace b200seq

@@ -12,7 +12,7 @@ request's slots (padded over requests), so admission, retirement and preemption 
 
 Layers need not be softmax attention with their own K/V.  Latent-attention layers page one latent vector per token
 (``attend_latent``), and a layer may read the pages another layer wrote; ``attend_mixed`` serves attention whose
-softmax weights are mixed across heads.  Recurrent mixers keep a fixed-size state per
+softmax weights are mixed across heads, ``attend_window`` sliding-window attention with a distance penalty and a sink.  Recurrent mixers keep a fixed-size state per
 request instead of pages: every request owns a *state row* for its lifetime (``recurrent_state`` hands out per-layer
 tensors ``[max_requests, ...]`` indexed by that row, zeroed when the row is given to a new request), and ``packed``
 describes the step's sequence boundaries and rows to the scan kernels.  Chunked prefill, continuous batching and
@@ -244,6 +244,26 @@ class DynamicInferenceContext:
         self.kernel_calls += 1
         return seqmix.mixed_attention_paged(q, kc, vc, self._block_table, self._tok_req, self._tok_len, self.block_size, scale,
                                             talk, gate, self._max_len)
+
+    def attend_window(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
+                      slopes: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                      out_scale: float = 1.0) -> torch.Tensor:
+        """Sliding-window grouped-query attention over the pages of cache ``layer``: ``q [T, H, d]``, new ``k [T, G, d]`` /
+        ``v [T, G, dv]`` (written into their pages first; ``v`` may be a strided view), a distance penalty per head
+        (``slopes [H]``), an optional sink in the softmax denominator and a per-head output gate ``[T, H]`` (pre-activation)
+        -> ``[T, H * dv]``.  A token sees the ``window`` last positions of its sequence (0: all).  fp32 and 16-bit caches."""
+        from ..ops import seqmix
+
+        if layer not in self.kv:
+            n_slots = self.num_blocks * self.block_size
+            self.kv[layer] = (torch.zeros(n_slots, *k.shape[1:], dtype=k.dtype, device=k.device),
+                              torch.zeros(n_slots, *v.shape[1:], dtype=v.dtype, device=v.device))
+        kc, vc = self.kv[layer]
+        kc[self._write_slots] = k
+        vc[self._write_slots] = v
+        self.kernel_calls += 1
+        return seqmix.window_attention_paged(q, kc, vc, self._block_table, self._tok_req, self._tok_len, self.block_size, scale,
+                                             window, slopes, sink, gate, out_scale)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:

@@ -30,6 +30,9 @@ class LanguageModelEmbedding(MegatronModule):
         super().__init__(config)
         self.vocab_size, self.max_sequence_length = vocab_size, max_sequence_length
         self.add_position_embedding = position_embedding_type == "learned_absolute"
+        # "sinusoidal": entry 2i of the embedding gains sin(p * base^(-2i / h)), entry 2i + 1 the cosine (fp32 angles); the
+        # result is fp32
+        self.sinusoidal = position_embedding_type == "sinusoidal"
         self.num_tokentypes = num_tokentypes
         self.scatter_to_sequence_parallel = scatter_to_sequence_parallel
         self.reduce_scatter_embeddings = ((not self.add_position_embedding) and num_tokentypes <= 0
@@ -50,6 +53,10 @@ class LanguageModelEmbedding(MegatronModule):
                 config.init_method(self.tokentype_embeddings.weight)
         else:
             self.tokentype_embeddings = None
+        if self.sinusoidal:
+            if config.hidden_size % 2:
+                raise ValueError("sinusoidal positions need an even hidden size")
+            self.register_buffer("sinusoid_freq", llama3_scaled_frequencies(config.hidden_size, 10000.0).to(dev), persistent=False)
         self.embedding_dropout = nn.Dropout(config.hidden_dropout)
 
     def zero_parameters(self):
@@ -67,6 +74,14 @@ class LanguageModelEmbedding(MegatronModule):
             emb = emb + self.tokentype_embeddings(tokentype_ids).permute(1, 0, 2)
         if self.config.fp32_residual_connection:
             emb = emb.float()
+        if self.sinusoidal:
+            from ...ops import seqmix
+
+            emb = emb.float().contiguous()                                   # [s, b, h]
+            s_, b_ = emb.shape[0], emb.shape[1]
+            pos = (torch.arange(s_, device=emb.device).unsqueeze(1).expand(s_, b_) if position_ids is None
+                   else position_ids.transpose(0, 1)).reshape(-1)
+            seqmix.add_sinusoid(emb.view(s_ * b_, -1), pos, self.sinusoid_freq)
         if self.config.sequence_parallel:
             if not self.reduce_scatter_embeddings and self.scatter_to_sequence_parallel:
                 emb = scatter_to_sequence_parallel_region(emb)

@@ -57,6 +57,13 @@ def _lerorax(path, params_dtype, device, **overrides):
     return load_model_dir(path, params_dtype, device, **overrides)
 
 
+@register_architecture("Domasun")
+def _domasun(path, params_dtype, device, **overrides):
+    from .domasun.loader import load_model_dir
+
+    return load_model_dir(path, params_dtype, device, **overrides)
+
+
 @register_architecture("GPTModel")
 def _gpt(path, params_dtype, device, **overrides):
     """A GPT / Llama-style folder: ``config.json`` holds ``TransformerConfig`` fields under ``transformer`` plus

@@ -141,6 +141,8 @@ class GroupedMLP(MegatronModule):
         return _expert_replica(sd)
 
     def _activation(self, inter):
+        if self.glu and getattr(self.config.activation_func, "fused_glu", False):     # takes the packed [gate | up] itself
+            return self.config.activation_func(inter)
         return ops.swiglu(inter) if (self.glu and self.config.activation_func is F.silu) else (
             self._glu(inter) if self.glu else self._act(inter))
 
@@ -177,9 +179,7 @@ class GroupedMLP(MegatronModule):
                 continue
             w1 = self.weight1[e * self.fc1_out:(e + 1) * self.fc1_out]
             w2 = self.weight2[e * h:(e + 1) * h]
-            inter = ops.linear(chunk, w1)
-            inter = ops.swiglu(inter) if (self.glu and self.config.activation_func is F.silu) else (
-                self._glu(inter) if self.glu else self._act(inter))
+            inter = self._activation(ops.linear(chunk, w1))
             outs.append(ops.linear(inter, w2))
         return torch.cat(outs, dim=0), None
 

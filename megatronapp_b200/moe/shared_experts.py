@@ -21,6 +21,8 @@ class SharedExpertMLP(MLP):
     def __init__(self, config, submodules, gate: bool = False):
         cfg = copy.copy(config)
         cfg.ffn_hidden_size = config.moe_shared_expert_intermediate_size
+        if getattr(config, "moe_shared_expert_activation_func", None) is not None:       # an activation of its own
+            cfg.activation_func = config.moe_shared_expert_activation_func
         super().__init__(cfg, submodules)
         self.use_shared_expert_gate = bool(gate)
         if gate:

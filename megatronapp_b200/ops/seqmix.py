@@ -134,19 +134,22 @@ def gated_head_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[to
 # short causal convolution with a carried window
 # ---------------------------------------------------------------------------
 
-def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor) -> torch.Tensor:
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor,
+                     bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``causal_conv`` followed by SiLU."""
-    return causal_conv(x, weight, pb, window, silu=True)
+    return causal_conv(x, weight, pb, window, silu=True, bias=bias)
 
 
-def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor, silu: bool = False) -> torch.Tensor:
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor, silu: bool = False,
+                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Depth-wise causal convolution over time, optionally followed by SiLU.  ``x [T, C]``, ``weight [C, taps]`` (last
-    column multiplies the current token), ``window [rows, taps - 1, C]``: the inputs that preceded each sequence's first
-    token of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs seen."""
+    column multiplies the current token), ``bias [C]`` (optional), ``window [rows, taps - 1, C]``: the inputs that preceded
+    each sequence's first token of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs
+    seen."""
     if x.is_cuda:
         kernel_calls["causal_conv_silu" if silu else "causal_conv"] += 1
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        ext().causal_conv(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), pb.cu, pb.slots, pb.tok_seq,
+        ext().causal_conv(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), bias, pb.cu, pb.slots, pb.tok_seq,
                           window, y, pb.max_len, bool(silu))
         return y
     taps = weight.shape[1]
@@ -158,6 +161,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: 
             continue
         seq = torch.cat([window[s].float(), x[a:b].float()], dim=0)                # [taps - 1 + n, C]
         y = sum(seq[j:j + (b - a)] * w[:, j] for j in range(taps))
+        if bias is not None:
+            y = y + bias.float()
         out.append(F.silu(y) if silu else y)
         if taps > 1:
             window[s] = seq[-(taps - 1):].to(window.dtype)
@@ -506,3 +511,173 @@ def clamped_glu(x: torch.Tensor, limit: float, alpha: float = 1.702, shift: floa
     g = torch.clamp(x[..., :F_].float(), max=limit)
     u = torch.clamp(x[..., F_:].float(), -limit, limit)
     return (g * torch.sigmoid(alpha * g) * (u + shift)).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------
+# several fp32 residual streams: update by a sublayer's output fused with the norm of the next sublayer's input
+# ---------------------------------------------------------------------------
+
+def stream_mix_norm(x: torch.Tensor, a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None,
+                    bias_a: Optional[torch.Tensor] = None, ls: Optional[torch.Tensor] = None, scale_a: float = 1.0,
+                    scale_b: float = 1.0, mix: Optional[torch.Tensor] = None, outc: Optional[torch.Tensor] = None,
+                    inp: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
+                    eps: float = 1e-5, out_dtype: Optional[torch.dtype] = None, center: bool = True):
+    """``x`` fp32 ``[T, S, W]``: ``S`` residual streams, updated in place.  With a pending sublayer output ``a [T, W]``
+    (and optionally a second branch ``b``)::
+
+        y = ls * (scale_a * (a + bias_a) + scale_b * b);   x_t <- sum_s mix[s, t] x_s + outc[t] * y   (all t at once)
+
+    then, with read weights ``inp [S]``: ``u = sum_s inp[s] x_s`` and ``h = norm(u) * weight + beta`` (layer norm when
+    ``center``, else RMS norm), in ``out_dtype``.  ``mix``, ``outc``, ``inp`` are fp32; everything is computed in fp32.
+    Returns ``(x, h or None)``."""
+    T, S, W = x.shape
+    if x.is_cuda:
+        kernel_calls["stream_mix_norm"] += 1
+        h = torch.empty(T, W, dtype=out_dtype or weight.dtype, device=x.device) if inp is not None else None
+        fix = lambda t: t if (t is None or t.stride(1) == 1) else t.contiguous()  # noqa: E731
+        ext().stream_mix_norm(x, fix(a), fix(b), bias_a, ls, float(scale_a), float(scale_b), mix, outc, inp, weight, beta, h,
+                              float(eps), bool(center))
+        return x, h
+    if a is not None:
+        y = a.float()
+        if bias_a is not None:
+            y = y + bias_a.float()
+        y = y * scale_a
+        if b is not None:
+            y = y + scale_b * b.float()
+        if ls is not None:
+            y = y * ls.float()
+        x.copy_(torch.einsum("st,nsw->ntw", mix.float(), x) + outc.float().view(1, S, 1) * y.unsqueeze(1))
+    if inp is None:
+        return x, None
+    u = torch.einsum("s,nsw->nw", inp.float(), x)
+    if center:
+        u = u - u.mean(-1, keepdim=True)
+    h = u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    if beta is not None:
+        h = h + beta.float()
+    return x, h.to(out_dtype or weight.dtype)
+
+
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -> torch.Tensor:
+    """``x`` fp32 ``[T, W]`` (in place): entry ``2i`` gains ``sin(positions[t] * freq[i])``, entry ``2i + 1`` the cosine;
+    ``freq`` fp32 ``[W / 2]``.  Angles are fp32."""
+    if x.is_cuda:
+        kernel_calls["add_sinusoid"] += 1
+        ext().add_sinusoid(x, positions.contiguous().long(), freq)
+        return x
+    ang = positions.float().unsqueeze(-1) * freq.float()
+    x[:, 0::2] += torch.sin(ang)
+    x[:, 1::2] += torch.cos(ang)
+    return x
+
+
+def head_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x [T, heads, d]`` (a column slice of a fused projection is fine): every head divided by its root mean square over
+    ``d`` (fp32 statistics), times ``weight [d]`` shared by the heads.  Returns a contiguous tensor in ``x``'s dtype."""
+    if x.is_cuda:
+        kernel_calls["head_rms_norm"] += 1
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        ext().head_rms_norm(_rows3(x), weight, y, float(eps))
+        return y
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------
+# paged grouped-query attention: sliding window, distance penalty per head, sink in the denominator, gate per head
+# ---------------------------------------------------------------------------
+
+def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                           tok_req: torch.Tensor, tok_len: torch.Tensor, block_size: int, scale: float, window: int = 0,
+                           slopes: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                           out_scale: float = 1.0) -> torch.Tensor:
+    """``q [T, H, d]`` against paged keys ``[slots, G, d]`` and values ``[slots, G, dv]``.  The token at position
+    ``i = tok_len[t] - 1`` sees the keys ``j`` of its own sequence with ``0 <= i - j < window`` (``window = 0``: all up to
+    ``i``)::
+
+        s_j = q . k_j * scale - slopes[h] * (i - j);     p_j = exp(s_j) / (sink + sum_j exp(s_j))
+
+    ``sink``: a key of score 0 without a value takes part in the normalisation.  ``gate [T, H]`` (pre-activation) multiplies
+    head ``h``'s output by its sigmoid; ``out_scale`` multiplies everything.  Scores, weights and sums are fp32.  Returns
+    ``[T, H * dv]`` in ``q``'s dtype."""
+    T, H, d = q.shape
+    G, dv = kcache.shape[1], vcache.shape[2]
+    if q.is_cuda:
+        kernel_calls["window_attention_paged"] += 1
+        o = torch.empty(T, H * dv, dtype=q.dtype, device=q.device)
+        ext().window_attention_paged(_rows3(q), kcache, vcache, block_table, tok_req, tok_len,
+                                     None if slopes is None else slopes.float().contiguous(),
+                                     None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()), o,
+                                     int(block_size), float(scale), int(window), bool(sink), float(out_scale))
+        return o
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    req, lens = tok_req.tolist(), tok_len.tolist()
+    rep = H // G
+    t = 0
+    while t < T:
+        e = t
+        while e + 1 < T and req[e + 1] == req[t]:
+            e += 1
+        L = max(lens[t:e + 1])
+        lo = max(0, min(lens[t:e + 1]) - window) if window > 0 else 0
+        pos = torch.arange(lo, L)
+        slots = block_table[req[t]].long()[pos // block_size] * block_size + pos % block_size
+        kk = kcache[slots].float().repeat_interleave(rep, dim=1)                        # [L - lo, H, d]
+        vv = vcache[slots].float().repeat_interleave(rep, dim=1)
+        s = torch.einsum("thd,lhd->htl", q[t:e + 1].float(), kk) * scale
+        qpos = torch.tensor(lens[t:e + 1]).view(1, -1, 1) - 1
+        dist = qpos - pos.view(1, 1, -1)
+        if slopes is not None:
+            s = s - slopes.float().view(H, 1, 1) * dist
+        vis = (dist >= 0) & ((dist < window) if window > 0 else torch.ones_like(dist, dtype=torch.bool))
+        s = s.masked_fill(~vis, float("-inf"))
+        m = s.amax(-1, keepdim=True)
+        m = torch.clamp(m, min=0.0) if sink else torch.where(torch.isinf(m), torch.zeros_like(m), m)
+        ex = torch.exp(s - m)
+        den = ex.sum(-1, keepdim=True) + (torch.exp(-m) if sink else 0.0)
+        P = ex / torch.where(den > 0, den, torch.ones_like(den))
+        o[t:e + 1] = torch.einsum("htl,lhv->thv", P, vv)
+        t = e + 1
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float()).unsqueeze(-1)
+    return (o * out_scale).reshape(T, H * dv).to(q.dtype)
+
+
+# ---------------------------------------------------------------------------
+# selective scan: one decay per channel and state, step size per channel
+# ---------------------------------------------------------------------------
+
+def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, B: torch.Tensor, C: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+                   pb: PackedBatch, state: torch.Tensor, z: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
+                   out_scale: float = 1.0) -> torch.Tensor:
+    """``x [T, C]``, step sizes before bias and softplus ``dt_pre [T, C]`` fp32, ``B, C [T, N]``, ``A_log [C, N]``, ``D [C]``,
+    ``state [rows, C, N]`` fp32 -> ``[T, C]`` in ``x``'s dtype.  Per channel ``c`` and state ``n``::
+
+        dt = softplus(dt_pre + dt_bias);   S[c, n] <- exp(-dt_c exp(A_log[c, n])) S[c, n] + dt_c x_c B_n
+        y_c = sum_n S[c, n] C_n + D_c x_c;   y <- y * silu(z) * out_scale
+
+    Step sizes, decays and the state are fp32."""
+    T, Cn = x.shape
+    N = B.shape[1]
+    if x.is_cuda:
+        kernel_calls["selective_scan"] += 1
+        y = torch.empty(T, Cn, dtype=x.dtype, device=x.device)
+        fix = lambda t: t if (t is None or t.stride(1) == 1) else t.contiguous()  # noqa: E731
+        ext().selective_scan(fix(x), fix(z), fix(B), fix(C), fix(dt_pre.float()), dt_bias, A_log.contiguous(), D, pb.cu, pb.slots,
+                             state, y, float(out_scale))
+        return y
+    xf, Bf, Cf = x.float(), B.float(), C.float()
+    dt = F.softplus(dt_pre.float() + (dt_bias.float() if dt_bias is not None else 0.0), threshold=20.0)
+    A = -torch.exp(A_log.float())
+    out = torch.empty(T, Cn, dtype=torch.float32)
+    for r in range(pb.num_seqs):
+        lo, hi, row = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
+        S = state[row].clone()
+        for t in range(lo, hi):
+            S = torch.exp(dt[t].unsqueeze(-1) * A) * S + (dt[t] * xf[t]).unsqueeze(-1) * Bf[t].unsqueeze(0)
+            out[t] = S @ Cf[t] + D.float() * xf[t]
+        state[row] = S
+    if z is not None:
+        out = out * F.silu(z.float())
+    return (out * out_scale).to(x.dtype)

@@ -141,3 +141,86 @@ class OutputNormF32Block(MegatronModule):
             return x
         _, y = self.final_layernorm(x, None)
         return y
+
+
+class StreamLayer(MegatronModule):
+    """Pre-norm layer over ``streams`` fp32 residual streams: each sublayer reads a weighted sum of the streams through its
+    layer norm and writes its (layer-scaled) output back into all of them (``norms.StreamConnection``).  With
+    ``learned_connections = False`` and one stream it is ``x <- x + ls1 * mixer(norm1(x)); x <- x + ls2 * mlp(norm2(x))``.
+    A sublayer's write is handed on as a ``StreamUpdate`` and fused into the next sublayer's read.  ``cache_index`` names the
+    cache / state a call uses, so one layer object can run at several depths of a block."""
+
+    def __init__(self, config, layer_number: int, mixer: nn.Module, mlp: Optional[nn.Module] = None, streams: int = 1,
+                 learned_connections: bool = True, layer_scale: bool = False):
+        super().__init__(config)
+        from .norms import StreamConnection
+
+        self.layer_number = layer_number
+        eps, W = config.layernorm_epsilon, config.hidden_size
+        self.mixer, self.mlp = mixer, mlp
+        self.mixer_conn = StreamConnection(config, W, streams, eps, learned_connections, layer_scale)
+        self.mlp_conn = StreamConnection(config, W, streams, eps, learned_connections, layer_scale) if mlp is not None else None
+        if mlp is not None and hasattr(mlp, "set_layer_number"):
+            mlp.set_layer_number(layer_number)
+
+    def forward(self, x, pending=None, inference_context=None, cache_index=None):
+        with _scope("transformer_layer", layer=self.layer_number):
+            x, h = self.mixer_conn.read(x, pending)
+            out, bias = self.mixer(h, inference_context=inference_context,
+                                   cache_index=self.layer_number if cache_index is None else cache_index)
+            if bias is not None:
+                out = out + bias
+            pending = self.mixer_conn.write(out)
+            if self.mlp is not None:
+                x, h = self.mlp_conn.read(x, pending)
+                out, bias = self.mlp(h)
+                if bias is not None:
+                    out = out + bias
+                pending = self.mlp_conn.write(out)
+        return x, pending
+
+
+class StreamBlock(MegatronModule):
+    """A stack of ``StreamLayer`` runs followed by the final layer norm of the sum of the streams.  ``layer_builders[i](i)``
+    builds layer object ``i``; ``runs`` lists, depth by depth, which object runs there (default: each once, in order), so a
+    span of layers can be repeated with the same weights; run ``k`` uses cache / state index ``k``.  The streams all start as
+    copies of the block's input.  ``tap(run, sum of the streams)`` receives the residual after every run."""
+
+    def __init__(self, config, layer_builders: List[Callable[[int], StreamLayer]], runs: Optional[List[int]] = None,
+                 streams: int = 1, post_process: bool = True):
+        super().__init__(config)
+        from .norms import StreamConnection
+
+        self.layers = nn.ModuleList([build(i) for i, build in enumerate(layer_builders)])
+        self.runs = list(range(len(self.layers))) if runs is None else [int(r) for r in runs]
+        if any(not 0 <= r < len(self.layers) for r in self.runs):
+            raise ValueError("a run names a layer that does not exist")
+        self.streams = int(streams)
+        self.final_layernorm = StreamConnection(config, config.hidden_size, streams, config.layernorm_epsilon,
+                                                learned=False) if post_process else None
+        self.input_tensor = None
+        self.tap = None
+
+    def set_input_tensor(self, t):
+        self.input_tensor = t
+
+    def forward(self, hidden_states, inference_context=None):
+        from .norms import _stream_apply
+
+        x = hidden_states if self.input_tensor is None else self.input_tensor
+        if x.dtype != torch.float32:
+            x = x.float()
+        if x.dim() == 3:                                            # [s, b, W]: every stream starts as the embedding output
+            x = x.unsqueeze(-2).repeat(1, 1, self.streams, 1)
+        pending = None
+        for k, r in enumerate(self.runs):
+            x, pending = self.layers[r](x, pending, inference_context=inference_context, cache_index=k)
+            if self.tap is not None:
+                x, _ = _stream_apply(x, pending, None)
+                pending = None
+                self.tap(k, x.sum(-2))
+        if self.final_layernorm is None:
+            x, _ = _stream_apply(x, pending, None) if pending is not None else (x, None)
+            return x
+        _, y = self.final_layernorm.read(x, pending)
+        return y
