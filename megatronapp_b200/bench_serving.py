@@ -1,7 +1,9 @@
 """Serving benchmark of the hybrid (Zikunex) design beside the closest existing model, a GPT decoder with grouped-query
 attention and the same feed-forwards, both through ``DynamicInferenceEngine.forward_tokens`` (``bench.py --serving``);
 with ``--serving-design lerorax`` the Lerorax design beside its closest existing model, Zikunex, at equal width, depth and
-head sizes, and the Lerorax kernels beside their like kernels.
+head sizes, and the Lerorax kernels beside their like kernels; with ``--serving-design domasun`` the Domasun design beside its
+closest existing model, Lerorax (two mixers side by side on a paged attention and a recurrent memory), and its kernels
+beside their like kernels.
 
 Two parts, random weights, bf16:
 
@@ -124,6 +126,37 @@ def build_lerorax(s, device):
     lcfg = LeroraxConfig.from_dict(lerorax_config(s))
     base = lcfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
     return LeroraxModel(lcfg, base).to(device).eval()
+
+
+def domasun_config(s):
+    """A Domasun stack at the sizes of ``s``: six layers of which the third to the fifth run twice in a row (eight runs), four
+    residual streams, sliding-window attention (a window of 1024) beside a selective scan of twice the width with 16 states, a
+    mixture of clamped gated experts with a gated shared expert."""
+    left = {"heads": s["heads"], "kv_heads": max(1, s["heads"] // 4), "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "mask": {"size": 1024}}
+    right = {"inner": 2 * s["width"], "state": 16, "dt_rank": max(8, s["width"] // 16), "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["shared_ff"], "limit": 7.0}}
+    n = s["layers"]
+    owned = n - 2 if n >= 6 else n
+    layers = [{"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 1.1}, "mlp": moe}
+              for _ in range(owned)]
+    cfg = {"architecture": "Domasun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "streams": 4,
+           "logit_softcap": 30.0, "layers": layers}
+    if owned < n:
+        cfg["loop"] = {"start": 2, "stop": 4, "times": 2}
+    return cfg
+
+
+def build_domasun(s, device):
+    from .models.domasun import DomasunConfig, DomasunModel
+    from .parallel import state as ps
+
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_model_parallel(1, 1)
+    dcfg = DomasunConfig.from_dict(domasun_config(s))
+    base = dcfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
+    return DomasunModel(dcfg, base).to(device).eval()
 
 
 def _engine(model, max_tokens, max_requests):
@@ -291,6 +324,95 @@ def kernel_numbers_lerorax(s, device):
     return out, roof
 
 
+def kernel_numbers_domasun(s, device):
+    """The kernels of the Domasun layers alone, each beside the like kernel of the closest model (Lerorax)."""
+    from .ops import seqmix
+    from .transformer.window_attention import distance_slopes
+
+    bench, out, roof = _kernel_bench(device)
+    H, d, W = s["heads"], s["dim"], s["width"]
+    G = max(1, H // 4)
+    bf = torch.bfloat16
+    rn = lambda *sh, **kw: torch.randn(*sh, device=device, **kw)  # noqa: E731
+    # -- decode attention: 64 requests x 2048 cached tokens of which a window of 1024 is visible; prefill: one prompt of 2048
+    R, L, bs, win = 64, 2048, 16, 1024
+    nblk = R * L // bs
+    table = torch.randperm(nblk, device=device).to(torch.int32).view(R, L // bs)
+    req = torch.arange(R, dtype=torch.int32, device=device)
+    lens = torch.full((R,), L, dtype=torch.int32, device=device)
+    kc, vc = rn(nblk * bs, G, d, dtype=bf), rn(nblk * bs, G, d, dtype=bf)
+    slopes = distance_slopes(H).to(device)
+    q, gate = rn(R, H, d, dtype=bf), rn(R, H, dtype=bf)
+    bench("window_attention_paged.decode", lambda: seqmix.window_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, win, slopes,
+                                                                                 True, gate),
+          R * win * G * d * 2 * 2, flops=R * win * H * d * 4, like="mixed_attention_paged.decode")
+    talk = rn(H, H) * 0.3
+    gate_m = rn(R, H * d, dtype=bf)
+    bench("mixed_attention_paged.decode", lambda: seqmix.mixed_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, talk, gate_m, L),
+          R * L * G * d * 2 * 2, flops=R * L * H * d * 4)
+    T = 2048
+    table1 = torch.randperm(T // bs, device=device).to(torch.int32).view(1, -1)
+    req1 = torch.zeros(T, dtype=torch.int32, device=device)
+    len1 = torch.arange(1, T + 1, dtype=torch.int32, device=device)
+    q1, gate1, gate1m = rn(T, H, d, dtype=bf), rn(T, H, dtype=bf), rn(T, H * d, dtype=bf)
+    pairs = win * (win + 1) / 2 + (T - win) * win                     # visible (query, key) pairs under the window
+    bench("window_attention_paged.prefill", lambda: seqmix.window_attention_paged(q1, kc, vc, table1, req1, len1, bs, d ** -0.5, win,
+                                                                                  slopes, True, gate1),
+          T * G * d * 4 + T * H * d * 4, flops=pairs * H * d * 4, like="mixed_attention_paged.prefill")
+    bench("mixed_attention_paged.prefill", lambda: seqmix.mixed_attention_paged(q1, kc, vc, table1, req1, len1, bs, d ** -0.5, talk, gate1m, T),
+          T * G * d * 4 + T * H * d * 6, flops=T * (T + 1) / 2 * H * d * 4)
+    # -- scans: decode (64 sequences x 1 token, state bound) and prefill (4 x 2048 tokens)
+    C, N = 2 * W, 16
+    dd = 64
+    for tag, R_, n in (("decode", 64, 1), ("prefill", 4, 2048)):
+        T_ = R_ * n
+        pb = seqmix.PackedBatch([i * n for i in range(R_ + 1)], list(range(R_)), device)
+        x, z, B, Cm = rn(T_, C, dtype=bf), rn(T_, C, dtype=bf), rn(T_, N, dtype=bf), rn(T_, N, dtype=bf)
+        dtp = rn(T_, C) - 2.0
+        A_log, D, dtb = (torch.rand(C, N, device=device) + 0.1).log().to(bf), rn(C, dtype=bf), rn(C, dtype=bf)
+        S = torch.zeros(R_, C, N, device=device)
+        bench(f"selective_scan.{tag}", lambda: seqmix.selective_scan(x, dtp, B, Cm, A_log, D, pb, S, z, dtb),
+              R_ * C * N * 8 + T_ * C * (2 + 2 + 4 + 2) + C * N * 2, flops=T_ * C * N * 6, like=f"gen_delta_scan.{tag}")
+        rr, k, v = rn(T_, H, dd, dtype=bf), rn(T_, H, dd, dtype=bf), rn(T_, H, dd, dtype=bf)
+        wp, ap, wb = rn(T_, H * dd, dtype=bf), rn(T_, H * dd, dtype=bf), rn(H * dd, dtype=bf)
+        Sd = torch.zeros(R_, H, dd, dd, device=device)
+        bench(f"gen_delta_scan.{tag}", lambda: seqmix.gen_delta_scan(rr, k, v, wp, ap, wb, pb, Sd, 0.6),
+              R_ * H * dd * dd * 8 + T_ * H * dd * 2 * 5 + T_ * H * dd * 4, flops=T_ * H * dd * dd * 10)
+    # -- stream update + norm, per-head norm, positions, convolution over 8192 tokens
+    T, S_ = 8192, 4
+    X = rn(T, S_, W)
+    a, b = rn(T, W, dtype=bf), rn(T, W, dtype=bf)
+    w = torch.ones(W, device=device, dtype=bf)
+    mix, outc, inp = torch.eye(S_, device=device), torch.ones(S_, device=device), torch.full((S_,), 0.25, device=device)
+    bench("stream_mix_norm (4 streams, two branches)",
+          lambda: seqmix.stream_mix_norm(X, a, b, w, w, 0.8, 1.1, mix, outc, inp, w, w, 1e-5), T * W * (S_ * 8 + 2 + 2 + 2),
+          like="norm_add (two branches)")
+    X1 = rn(T, 1, W)
+    bench("stream_mix_norm (1 stream)", lambda: seqmix.stream_mix_norm(X1, a, None, None, w, 1.0, 1.0, mix[:1, :1].contiguous(), outc[:1],
+                                                                      outc[:1], w, w, 1e-5), T * W * (8 + 2 + 2), like="add_rms_norm")
+    x = rn(T, W)
+    bench("norm_add (two branches)", lambda: seqmix.norm_add(x, a, w, 1e-5, bf, 1.0, b, w, w), T * W * (4 + 4 + 2 + 2 + 2))
+    bench("add_rms_norm", lambda: seqmix.add_rms_norm(x, a, w, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+    qk = rn(T, (H + G) * d + H, dtype=bf)
+    wn = torch.ones(d, device=device, dtype=bf)
+    bench("head_rms_norm (q and k)", lambda: (seqmix.head_rms_norm(qk[:, :H * d].view(T, H, d), wn, 1e-5),
+                                             seqmix.head_rms_norm(qk[:, H * d:(H + G) * d].view(T, G, d), wn, 1e-5)),
+          T * (H + G) * d * 4, like="norm_rope")
+    wq, wk = torch.ones(H * d, device=device, dtype=bf), torch.ones(G * d, device=device, dtype=bf)
+    pos = torch.arange(T, device=device)
+    inv = torch.rand(d // 4, device=device)
+    bench("norm_rope", lambda: seqmix.norm_rope(qk[:, :H * d], qk[:, H * d:(H + G) * d], wq, wk, pos, inv, d, d // 2, 1e-5),
+          T * (H + G) * d * 4)
+    freq = torch.rand(W // 2, device=device)
+    bench("add_sinusoid", lambda: seqmix.add_sinusoid(x, pos, freq), T * W * 8, like="add_rms_norm")
+    xc, wc, cb = rn(T, C, dtype=bf), rn(C, 4, dtype=bf), rn(C, dtype=bf)
+    pbc = seqmix.PackedBatch([0, T], [0], device)
+    winc = torch.zeros(1, 3, C, device=device, dtype=bf)
+    bench("causal_conv_silu (bias)", lambda: seqmix.causal_conv_silu(xc, wc, pbc, winc, cb), T * C * 4, like="causal_conv_silu")
+    bench("causal_conv_silu", lambda: seqmix.causal_conv_silu(xc, wc, pbc, winc), T * C * 4)
+    return out, roof
+
+
 def kernel_numbers(s, device):
     """Every new kernel alone and its like kernel: time, achieved bytes/s (or flop/s) and the fraction of the roofline."""
     from . import ops
@@ -415,8 +537,9 @@ def run(args):
                                                            "timings rewrite a 160 MB buffer between launches")}
     design = getattr(args, "serving_design", "zikunex")
     res["design"] = design
-    pairs = (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)) if design == "zikunex" else \
-        (("lerorax", build_lerorax), ("zikunex", build_zikunex))
+    pairs = {"zikunex": (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)),
+             "lerorax": (("lerorax", build_lerorax), ("zikunex", build_zikunex)),
+             "domasun": (("domasun", build_domasun), ("lerorax", build_lerorax))}[design]
     with torch.no_grad():
         for name, build in pairs:
             t0 = time.time()
@@ -428,6 +551,7 @@ def run(args):
             del model
             torch.cuda.empty_cache()
         if not getattr(args, "serving_models_only", False):
-            res["kernels"], res["roofline"] = (kernel_numbers if design == "zikunex" else kernel_numbers_lerorax)(s, dev)
+            fn = {"zikunex": kernel_numbers, "lerorax": kernel_numbers_lerorax, "domasun": kernel_numbers_domasun}[design]
+            res["kernels"], res["roofline"] = fn(s, dev)
     print(json.dumps(res), flush=True)
     return res
