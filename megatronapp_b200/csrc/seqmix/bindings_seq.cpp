@@ -431,7 +431,7 @@ void head_rms_norm(const Tensor& x, const Tensor& w, Tensor y, double eps) {
 
 void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const Tensor& block_table, const Tensor& tok_req,
                             const Tensor& tok_len, c10::optional<Tensor> slopes, c10::optional<Tensor> gate, Tensor out, int64_t block_size,
-                            double scale, int64_t window, bool sink, double out_scale) {
+                            double scale, int64_t window, bool sink, double out_scale, int64_t max_len) {
   const bool bf16 = act_is_bf16(q, "q");
   check_rows(q, "q");
   TORCH_CHECK(kcache.scalar_type() == q.scalar_type() && vcache.scalar_type() == q.scalar_type() && kcache.dim() == 3 && vcache.dim() == 3 &&
@@ -461,9 +461,19 @@ void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor&
   p.scale = static_cast<float>(scale); p.out_scale = static_cast<float>(out_scale);
   p.window = static_cast<int>(window); p.sink = sink ? 1 : 0;
   c10::cuda::CUDAGuard g(q.device());
+  p.n_splits = 1;
+  Tensor ws;
+  if (max_len > 0 && block_table.size(0) == q.size(0)) {     // one token per sequence: a decoding batch
+    const int keys = window > 0 ? static_cast<int>(std::min<int64_t>(window, max_len)) : static_cast<int>(max_len);
+    p.n_splits = b200seq::window_attention_splits(p.H, p.G, p.n_tok, keys);
+    if (p.n_splits > 1) {
+      ws = torch::empty({q.size(0), p.H, p.n_splits, p.dv + 2}, q.options().dtype(at::kFloat));
+      p.ws = ws.data_ptr<float>();
+    }
+  }
   TORCH_CHECK(b200seq::window_attention_paged(p, bf16, cur_stream()), "window_attention_paged: no kernel instance for heads ", p.H, " / ",
               p.G, ", dims ", p.d, " / ", p.dv);
-  count(); check_last_error("window_attention_paged");
+  count(p.n_splits > 1 ? 2 : 1); check_last_error("window_attention_paged");
 }
 
 void selective_scan(const Tensor& x, c10::optional<Tensor> z, const Tensor& B, const Tensor& Cm, const Tensor& dt_pre,

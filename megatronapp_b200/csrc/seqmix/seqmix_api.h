@@ -145,6 +145,8 @@ struct WindowAttnArgs {
   int n_tok, H, G, d, dv, block_size, max_blocks;
   int window;                     // 0: every earlier key is visible
   int sink;                       // 1: one is added to the softmax denominator
+  int n_splits;                   // > 1 (one token per sequence only): the visible keys are cut over that many CTAs
+  float* ws;                      // [T, H, n_splits, dv + 2] when n_splits > 1
   int QB, HC;                     // filled by the launcher
   float scale, out_scale;
 };
@@ -166,6 +168,8 @@ void add_sinusoid(float* x, const int64_t* positions, const float* freq, int n_t
 void head_rms_norm(const void* x, int64_t ldx, const void* w, void* y, int n_tok, int heads, int d, float eps, bool bf16,
                    cudaStream_t s);
 bool window_attention_paged(const WindowAttnArgs& p, bool bf16, cudaStream_t s);
+// key splits for a batch of n_tok single-token sequences whose longest visible context is max_keys
+int window_attention_splits(int H, int G, int n_tok, int max_keys);
 bool selective_scan(const SelScanArgs& p, int R, bool bf16, cudaStream_t s);
 
 }  // namespace b200seq

@@ -111,6 +111,97 @@ __global__ void __launch_bounds__(256) stream_mix_norm_kernel(StreamNormArgs p) 
   }
 }
 
+// Four columns per thread and the number of streams known at compile time (W a multiple of 4, rows 16-byte aligned).
+template <typename T> __device__ __forceinline__ float4 ld4(const T* p);
+template <> __device__ __forceinline__ float4 ld4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T> __device__ __forceinline__ void st4(T* p, float4 v);
+template <> __device__ __forceinline__ void st4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float4 f4_fma(float a, float4 x, float4 y) {
+  return make_float4(fmaf(a, x.x, y.x), fmaf(a, x.y, y.y), fmaf(a, x.z, y.z), fmaf(a, x.w, y.w));
+}
+__device__ __forceinline__ float4 f4_mul(float4 x, float4 y) { return make_float4(x.x * y.x, x.y * y.y, x.z * y.z, x.w * y.w); }
+
+template <typename T, int S>
+__global__ void __launch_bounds__(256) stream_mix_norm_vec_kernel(StreamNormArgs p) {
+  extern __shared__ __align__(16) float su[];        // [W]
+  __shared__ float red[32];
+  const int W = p.W;
+  const int64_t row = blockIdx.x;
+  float* X = p.x + row * S * W;
+  const T* a = static_cast<const T*>(p.a);
+  const T* b = static_cast<const T*>(p.b);
+  const T* ba = static_cast<const T*>(p.bias_a);
+  const T* ls = static_cast<const T*>(p.ls);
+  float cmix[S * S], cout_[S], cin[S];
+#pragma unroll
+  for (int i = 0; i < S * S; ++i) cmix[i] = a != nullptr ? p.mix[i] : 0.f;
+#pragma unroll
+  for (int i = 0; i < S; ++i) { cout_[i] = a != nullptr ? p.outc[i] : 0.f; cin[i] = p.inp != nullptr ? p.inp[i] : 0.f; }
+  float sum = 0.f;
+  for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+    float4 xs[S];
+#pragma unroll
+    for (int s = 0; s < S; ++s) xs[s] = *reinterpret_cast<const float4*>(X + static_cast<int64_t>(s) * W + c);
+    if (a != nullptr) {
+      float4 y = ld4(a + row * p.lda + c);
+      if (ba != nullptr) { const float4 bv = ld4(ba + c); y = make_float4(y.x + bv.x, y.y + bv.y, y.z + bv.z, y.w + bv.w); }
+      y = make_float4(y.x * p.scale_a, y.y * p.scale_a, y.z * p.scale_a, y.w * p.scale_a);
+      if (b != nullptr) y = f4_fma(p.scale_b, ld4(b + row * p.ldb + c), y);
+      if (ls != nullptr) y = f4_mul(y, ld4(ls + c));
+      float4 nx[S];
+#pragma unroll
+      for (int t = 0; t < S; ++t) {
+        float4 v = make_float4(cout_[t] * y.x, cout_[t] * y.y, cout_[t] * y.z, cout_[t] * y.w);
+#pragma unroll
+        for (int s = 0; s < S; ++s) v = f4_fma(cmix[s * S + t], xs[s], v);
+        nx[t] = v;
+      }
+#pragma unroll
+      for (int t = 0; t < S; ++t) { xs[t] = nx[t]; *reinterpret_cast<float4*>(X + static_cast<int64_t>(t) * W + c) = nx[t]; }
+    }
+    if (p.inp != nullptr) {
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s = 0; s < S; ++s) u = f4_fma(cin[s], xs[s], u);
+      *reinterpret_cast<float4*>(su + c) = u;
+      sum += (u.x + u.y) + (u.z + u.w);
+    }
+  }
+  if (p.inp == nullptr) return;
+  const T* w = static_cast<const T*>(p.w);
+  const T* beta = static_cast<const T*>(p.beta);
+  T* h = static_cast<T*>(p.h) + row * W;
+  float mean = 0.f;
+  if (beta != nullptr || p.center) mean = block_sum(sum, red) / static_cast<float>(W);
+  else __syncthreads();
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+    const float4 u = *reinterpret_cast<const float4*>(su + c);
+    const float d0 = u.x - mean, d1 = u.y - mean, d2 = u.z - mean, d3 = u.w - mean;
+    ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(W) + p.eps);
+  for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+    const float4 u = *reinterpret_cast<const float4*>(su + c);
+    const float4 wv = ld4(w + c);
+    float4 v = make_float4((u.x - mean) * rstd * wv.x, (u.y - mean) * rstd * wv.y, (u.z - mean) * rstd * wv.z, (u.w - mean) * rstd * wv.w);
+    if (beta != nullptr) { const float4 bv = ld4(beta + c); v = make_float4(v.x + bv.x, v.y + bv.y, v.z + bv.z, v.w + bv.w); }
+    st4(h + c, v);
+  }
+}
+
 // x [T, W] (fp32, in place): x[t, 2i] += sin(pos_t * f_i), x[t, 2i + 1] += cos(pos_t * f_i)
 __global__ void add_sinusoid_kernel(float* __restrict__ x, const int64_t* __restrict__ positions, const float* __restrict__ freq,
                                     int64_t n_pairs_total, int half) {
@@ -149,30 +240,71 @@ __global__ void __launch_bounds__(128) head_rms_norm_kernel(const T* __restrict_
 // all keys up to i); score = q . k * scale - slope[h] * (i - j); weights exp(s_j) / (sink + sum_j exp(s_j)) where the sink
 // (0 or 1) is a key of score 0 without a value; the head's output is multiplied by sigmoid(gate[t, h]) and out_scale.
 //
-// grid (query blocks, kv heads, head chunks).  A CTA takes QB consecutive packed tokens and HC heads of one kv head: its
-// QB * HC <= 32 (query, head) pairs are spread over 8 warps, 4 pairs each.  Keys and values of a tile of 32 cached tokens are
-// staged in shared memory as fp32 once for all pairs.  Scores: a lane owns one key of the tile and walks the head dimension
-// for the warp's 4 pairs at once; the online softmax state (m, l) is kept per pair; values: a lane owns channels
-// lane, lane + 32, ... of the 4 accumulators.  A block of tokens that straddles sequences walks them one after the other.
+// grid (query blocks, kv heads, head chunks x key splits).  A CTA takes QB consecutive packed tokens and HC heads of one kv
+// head: its QB * HC <= 64 (query, head) pairs are dealt round robin to 8 warps, up to 8 per warp.  Keys and values of a tile of
+// 32 cached tokens are staged in shared memory as fp32 once for all pairs.  Scores: a lane owns one key of the tile and walks
+// the head dimension for all pairs of its warp at once (the queries of a warp lie pair-interleaved, so one 16-byte broadcast
+// read brings a channel of four pairs); the online softmax state (m, l) is kept per pair; values: a lane owns channels
+// lane, lane + 32, ... of the accumulators.  A block of tokens that straddles sequences walks them one after the other.
+// Decoding batches (one token per sequence) split the visible keys over several CTAs (n_splits), which leave (m, l, sum) in a
+// workspace for the merge kernel.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kWinWarps = 8, kWinPairs = 4, kWinTile = 32;
+constexpr int kWinWarps = 8, kWinSlots = 8, kWinTile = 32;
+
+template <typename T>
+__device__ __forceinline__ void stage_rows(float* dst, int ld_dst, const T* cache, const int* table, int block_size, int G, int g,
+                                           int width, int k0, int n_keys) {
+  for (int i = threadIdx.x; i < n_keys * width; i += blockDim.x) {
+    const int j = i / width, c = i % width, key = k0 + j;
+    const int64_t slot = static_cast<int64_t>(table[key / block_size]) * block_size + key % block_size;
+    dst[j * ld_dst + c] = ld(cache + (slot * G + g) * width + c);
+  }
+}
+// 16-byte loads of bf16 rows (width a multiple of 8, rows 16-byte aligned)
+__device__ __forceinline__ void stage_rows_vec(float* dst, int ld_dst, const __nv_bfloat16* cache, const int* table, int block_size,
+                                               int G, int g, int width, int k0, int n_keys) {
+  const int per_row = width >> 3;
+  for (int i = threadIdx.x; i < n_keys * per_row; i += blockDim.x) {
+    const int j = i / per_row, c = (i % per_row) << 3, key = k0 + j;
+    const int64_t slot = static_cast<int64_t>(table[key / block_size]) * block_size + key % block_size;
+    const uint4 raw = *reinterpret_cast<const uint4*>(cache + (slot * G + g) * width + c);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float* o = dst + j * ld_dst + c;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h2[e]); o[2 * e] = f.x; o[2 * e + 1] = f.y; }
+  }
+}
+template <typename T>
+__device__ __forceinline__ void stage_tile(float* dst, int ld_dst, const T* cache, const int* table, int block_size, int G, int g,
+                                           int width, int k0, int n_keys, bool vec) {
+  stage_rows<T>(dst, ld_dst, cache, table, block_size, G, g, width, k0, n_keys);
+}
+template <>
+__device__ __forceinline__ void stage_tile<__nv_bfloat16>(float* dst, int ld_dst, const __nv_bfloat16* cache, const int* table,
+                                                          int block_size, int G, int g, int width, int k0, int n_keys, bool vec) {
+  if (vec) stage_rows_vec(dst, ld_dst, cache, table, block_size, G, g, width, k0, n_keys);
+  else stage_rows<__nv_bfloat16>(dst, ld_dst, cache, table, block_size, G, g, width, k0, n_keys);
+}
 
 template <typename T, int DVR>
 __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(WindowAttnArgs p) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int d = p.d, dv = p.dv, ldk = d + 1, ldv = dv;
-  float* sq = smem;                                        // [32 pairs][d]
-  float* sk = sq + 32 * d;                                 // [tile][d + 1]
+  float* sq = smem;                                        // [warps][d][slots]
+  float* sk = sq + kWinWarps * kWinSlots * d;              // [tile][d + 1]
   float* sv = sk + kWinTile * ldk;                         // [tile][dv]
-  float* sp = sv + kWinTile * ldv;                         // [warps][pairs][tile]
+  float* sp = sv + kWinTile * ldv;                         // [warps][tile][slots]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y, rep = p.H / p.G;
-  const int h_lo = blockIdx.z * p.HC, n_heads = min(p.HC, rep - h_lo);     // heads of this chunk, relative to the group
+  const int chunk = blockIdx.z / p.n_splits, split = blockIdx.z % p.n_splits;
+  const int h_lo = chunk * p.HC, n_heads = min(p.HC, rep - h_lo);          // heads of this chunk, relative to the group
   const int t0 = blockIdx.x * p.QB, t1 = min(p.n_tok, t0 + p.QB);
   const T* qbase = static_cast<const T*>(p.q);
   const T* kc = static_cast<const T*>(p.kcache);
   const T* vc = static_cast<const T*>(p.vcache);
-  float* mysp = sp + warp * kWinPairs * kWinTile;
+  const bool vec_k = (d & 7) == 0, vec_v = (dv & 7) == 0;
+  float* mysp = sp + warp * kWinTile * kWinSlots;
+  const float* myq = sq + warp * kWinSlots * d;
 
   int seg = t0;
   while (seg < t1) {
@@ -180,91 +312,105 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
     int seg_end = seg + 1;
     while (seg_end < t1 && p.tok_req[seg_end] == r) ++seg_end;
     const int nq = seg_end - seg, n_pairs = nq * n_heads;
+    const int ns = warp < n_pairs ? (n_pairs - warp + kWinWarps - 1) / kWinWarps : 0;       // pairs of this warp
     const int* table = p.block_table + static_cast<int64_t>(r) * p.max_blocks;
     const int len_first = p.tok_len[seg], len_last = p.tok_len[seg_end - 1];
-    const int k_begin = p.window > 0 ? max(0, len_first - p.window) : 0, k_end = len_last;
+    int k_begin = p.window > 0 ? max(0, len_first - p.window) : 0, k_end = len_last;
+    if (p.n_splits > 1) {                                  // one query per CTA: its keys are cut into n_splits runs of whole tiles
+      const int per = ((k_end - k_begin + p.n_splits - 1) / p.n_splits + kWinTile - 1) / kWinTile * kWinTile;
+      k_begin += split * per;
+      k_end = min(k_end, k_begin + per);
+    }
     __syncthreads();                                       // the previous segment's reads of sq are over
     for (int i = threadIdx.x; i < n_pairs * d; i += blockDim.x) {
       const int pr = i / d, c = i % d, qi = pr / n_heads, hh = pr % n_heads;
-      sq[pr * d + c] = ld(qbase + static_cast<int64_t>(seg + qi) * p.ldq + static_cast<int64_t>(g * rep + h_lo + hh) * d + c) * p.scale;
+      sq[((pr % kWinWarps) * d + c) * kWinSlots + pr / kWinWarps] =
+          ld(qbase + static_cast<int64_t>(seg + qi) * p.ldq + static_cast<int64_t>(g * rep + h_lo + hh) * d + c) * p.scale;
     }
-    // per-pair state of this warp
-    float m[kWinPairs], l[kWinPairs], acc[kWinPairs][DVR], slope[kWinPairs];
-    int pos[kWinPairs], lo[kWinPairs];
+    float m[kWinSlots], l[kWinSlots], acc[kWinSlots][DVR], slope[kWinSlots];
+    int pos[kWinSlots], lo[kWinSlots];
+    const bool with_sink = p.sink && split == 0;
 #pragma unroll
-    for (int u = 0; u < kWinPairs; ++u) {
-      const int pr = warp * kWinPairs + u;
-      m[u] = p.sink ? 0.f : -INFINITY;
-      l[u] = p.sink ? 1.f : 0.f;
+    for (int u = 0; u < kWinSlots; ++u) {
+      m[u] = with_sink ? 0.f : -INFINITY;
+      l[u] = with_sink ? 1.f : 0.f;
 #pragma unroll
       for (int k = 0; k < DVR; ++k) acc[u][k] = 0.f;
-      if (pr < n_pairs) {
-        const int qi = pr / n_heads, hh = pr % n_heads;
+      pos[u] = -1; lo[u] = 0; slope[u] = 0.f;
+      if (u < ns) {
+        const int pr = warp + u * kWinWarps, qi = pr / n_heads, hh = pr % n_heads;
         pos[u] = p.tok_len[seg + qi] - 1;
         lo[u] = p.window > 0 ? max(0, pos[u] + 1 - p.window) : 0;
         slope[u] = p.slopes != nullptr ? p.slopes[g * rep + h_lo + hh] : 0.f;
-      } else { pos[u] = -1; lo[u] = 0; slope[u] = 0.f; }
+      }
     }
     for (int k0 = k_begin; k0 < k_end; k0 += kWinTile) {
       const int n_keys = min(kWinTile, k_end - k0);
       __syncthreads();                                     // the previous tile (and sq) is settled
-      for (int i = threadIdx.x; i < n_keys * d; i += blockDim.x) {
-        const int j = i / d, c = i % d, key = k0 + j;
-        const int64_t slot = static_cast<int64_t>(table[key / p.block_size]) * p.block_size + key % p.block_size;
-        sk[j * ldk + c] = ld(kc + (slot * p.G + g) * d + c);
-      }
-      for (int i = threadIdx.x; i < n_keys * dv; i += blockDim.x) {
-        const int j = i / dv, c = i % dv, key = k0 + j;
-        const int64_t slot = static_cast<int64_t>(table[key / p.block_size]) * p.block_size + key % p.block_size;
-        sv[j * ldv + c] = ld(vc + (slot * p.G + g) * dv + c);
-      }
+      stage_tile<T>(sk, ldk, kc, table, p.block_size, p.G, g, d, k0, n_keys, vec_k);
+      stage_tile<T>(sv, ldv, vc, table, p.block_size, p.G, g, dv, k0, n_keys, vec_v);
       __syncthreads();
-      // does any pair of this warp see a key of this tile?
-      bool any = false;
+      bool any = false;                                    // does any pair of this warp see a key of this tile?
 #pragma unroll
-      for (int u = 0; u < kWinPairs; ++u) any = any || (pos[u] >= k0 && lo[u] < k0 + n_keys);
+      for (int u = 0; u < kWinSlots; ++u) any = any || (u < ns && pos[u] >= k0 && lo[u] < k0 + n_keys);
       if (!any) continue;
-      float s[kWinPairs];
+      float s[kWinSlots];
 #pragma unroll
-      for (int u = 0; u < kWinPairs; ++u) s[u] = 0.f;
+      for (int u = 0; u < kWinSlots; ++u) s[u] = 0.f;
       if (lane < n_keys) {
         const float* krow = sk + lane * ldk;
-        const float* q0 = sq + (warp * kWinPairs) * d;
-        for (int c = 0; c < d; ++c) {
-          const float kv = krow[c];
-#pragma unroll
-          for (int u = 0; u < kWinPairs; ++u) s[u] = fmaf(q0[u * d + c], kv, s[u]);
+        if (ns > 4) {
+          for (int c = 0; c < d; ++c) {
+            const float kv = krow[c];
+            const float4 qa = *reinterpret_cast<const float4*>(myq + c * kWinSlots);
+            const float4 qb = *reinterpret_cast<const float4*>(myq + c * kWinSlots + 4);
+            s[0] = fmaf(qa.x, kv, s[0]); s[1] = fmaf(qa.y, kv, s[1]); s[2] = fmaf(qa.z, kv, s[2]); s[3] = fmaf(qa.w, kv, s[3]);
+            s[4] = fmaf(qb.x, kv, s[4]); s[5] = fmaf(qb.y, kv, s[5]); s[6] = fmaf(qb.z, kv, s[6]); s[7] = fmaf(qb.w, kv, s[7]);
+          }
+        } else {
+          for (int c = 0; c < d; ++c) {
+            const float kv = krow[c];
+            const float4 qa = *reinterpret_cast<const float4*>(myq + c * kWinSlots);
+            s[0] = fmaf(qa.x, kv, s[0]); s[1] = fmaf(qa.y, kv, s[1]); s[2] = fmaf(qa.z, kv, s[2]); s[3] = fmaf(qa.w, kv, s[3]);
+          }
         }
       }
       const int key = k0 + lane;
+      float pw[kWinSlots];
 #pragma unroll
-      for (int u = 0; u < kWinPairs; ++u) {
-        const bool vis = lane < n_keys && key <= pos[u] && key >= lo[u];
-        const float sc = vis ? s[u] - slope[u] * static_cast<float>(pos[u] - key) : -INFINITY;
-        const float m_new = fmaxf(m[u], warp_max(sc));
-        float pw = 0.f, corr = 1.f;
-        if (m_new != -INFINITY) {
-          pw = vis ? expf(sc - m_new) : 0.f;
-          corr = expf(m[u] - m_new);                      // m = -inf: 0, and l and acc are 0 then
+      for (int u = 0; u < kWinSlots; ++u) {
+        pw[u] = 0.f;
+        if (u < ns) {
+          const bool vis = lane < n_keys && key <= pos[u] && key >= lo[u];
+          const float sc = vis ? s[u] - slope[u] * static_cast<float>(pos[u] - key) : -INFINITY;
+          const float m_new = fmaxf(m[u], warp_max(sc));
+          float corr = 1.f;
+          if (m_new != -INFINITY) {
+            pw[u] = vis ? expf(sc - m_new) : 0.f;
+            corr = expf(m[u] - m_new);                    // m = -inf: 0, and l and acc are 0 then
+          }
+          l[u] = l[u] * corr + warp_sum(pw[u]);
+          m[u] = m_new;
+#pragma unroll
+          for (int k = 0; k < DVR; ++k) acc[u][k] *= corr;
         }
-        l[u] = l[u] * corr + warp_sum(pw);
-        m[u] = m_new;
-#pragma unroll
-        for (int k = 0; k < DVR; ++k) acc[u][k] *= corr;
-        mysp[u * kWinTile + lane] = pw;
       }
+      *reinterpret_cast<float4*>(mysp + lane * kWinSlots) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+      *reinterpret_cast<float4*>(mysp + lane * kWinSlots + 4) = make_float4(pw[4], pw[5], pw[6], pw[7]);
       __syncwarp();
       for (int j = 0; j < n_keys; ++j) {
-        float pj[kWinPairs];
-#pragma unroll
-        for (int u = 0; u < kWinPairs; ++u) pj[u] = mysp[u * kWinTile + j];
+        const float4 pa = *reinterpret_cast<const float4*>(mysp + j * kWinSlots);
+        float4 pb = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ns > 4) pb = *reinterpret_cast<const float4*>(mysp + j * kWinSlots + 4);
+        const float pj[kWinSlots] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
 #pragma unroll
         for (int k = 0; k < DVR; ++k) {
           const int c = lane + 32 * k;
           if (c < dv) {
             const float vv = sv[j * ldv + c];
 #pragma unroll
-            for (int u = 0; u < kWinPairs; ++u) acc[u][k] = fmaf(pj[u], vv, acc[u][k]);
+            for (int u = 0; u < kWinSlots; ++u)
+              if (u < 4 || ns > 4) acc[u][k] = fmaf(pj[u], vv, acc[u][k]);
           }
         }
       }
@@ -274,11 +420,20 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
     T* out = static_cast<T*>(p.out);
     const T* gate = static_cast<const T*>(p.gate);
 #pragma unroll
-    for (int u = 0; u < kWinPairs; ++u) {
-      const int pr = warp * kWinPairs + u;
-      if (pr >= n_pairs) continue;
-      const int qi = pr / n_heads, hh = pr % n_heads, head = g * rep + h_lo + hh;
+    for (int u = 0; u < kWinSlots; ++u) {
+      if (u >= ns) continue;
+      const int pr = warp + u * kWinWarps, qi = pr / n_heads, hh = pr % n_heads, head = g * rep + h_lo + hh;
       const int64_t t = seg + qi;
+      if (p.n_splits > 1) {                                // (m, l, unnormalised sum) for the merge kernel
+        float* w = p.ws + ((t * p.H + head) * p.n_splits + split) * (dv + 2);
+        if (lane == 0) { w[0] = m[u]; w[1] = l[u]; }
+#pragma unroll
+        for (int k = 0; k < DVR; ++k) {
+          const int c = lane + 32 * k;
+          if (c < dv) w[2 + c] = acc[u][k];
+        }
+        continue;
+      }
       float f = p.out_scale / (l[u] > 0.f ? l[u] : 1.f);
       if (gate != nullptr) f *= sigmoidf_(ld(gate + t * p.ldg + head));
 #pragma unroll
@@ -288,6 +443,34 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
       }
     }
     seg = seg_end;
+  }
+}
+
+// one warp per (token, head): the partial results of the key splits become the head's output
+template <typename T>
+__global__ void __launch_bounds__(128) window_attention_merge_kernel(WindowAttnArgs p) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (row >= static_cast<int64_t>(p.n_tok) * p.H) return;
+  const int lane = threadIdx.x & 31, dv = p.dv;
+  const int64_t t = row / p.H;
+  const int head = static_cast<int>(row % p.H);
+  const float* w = p.ws + row * p.n_splits * (dv + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, w[s * (dv + 2)]);
+  float L = 0.f;
+  for (int s = 0; s < p.n_splits; ++s) {
+    const float ms = w[s * (dv + 2)];
+    if (ms != -INFINITY) L += w[s * (dv + 2) + 1] * expf(ms - M);
+  }
+  float f = p.out_scale / (L > 0.f ? L : 1.f);
+  if (p.gate != nullptr) f *= sigmoidf_(ld(static_cast<const T*>(p.gate) + t * p.ldg + head));
+  for (int c = lane; c < dv; c += 32) {
+    float a = 0.f;
+    for (int s = 0; s < p.n_splits; ++s) {
+      const float ms = w[s * (dv + 2)];
+      if (ms != -INFINITY) a = fmaf(w[s * (dv + 2) + 2 + c], expf(ms - M), a);
+    }
+    st(static_cast<T*>(p.out) + row * dv + c, a * f);
   }
 }
 
@@ -306,7 +489,9 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelScanArgs
   const int N = p.N;
   float* sdt = smem;                                 // [chunk][32]
   float* sx = sdt + kSelChunk * kSelCh;              // [chunk][32]
-  float* sB = sx + kSelChunk * kSelCh;               // [chunk][N]
+  float* sz = sx + kSelChunk * kSelCh;               // [chunk][32]  silu(z) * out_scale
+  float* sy = sz + kSelChunk * kSelCh;               // [chunk][32]  outputs of the round
+  float* sB = sy + kSelChunk * kSelCh;               // [chunk][N]
   float* sC = sB + kSelChunk * N;                    // [chunk][N]
   const int r = blockIdx.y, part = threadIdx.x & (kSelParts - 1), cl = threadIdx.x >> 2;
   const int c0 = blockIdx.x * kSelCh, c = c0 + cl;
@@ -324,7 +509,8 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelScanArgs
   for (int i = 0; i < NS; ++i) {
     const int n = part + kSelParts * i;
     const bool ok = live && n < N;
-    A[i] = ok ? -expf(ld(static_cast<const T*>(p.A_log) + static_cast<int64_t>(c) * N + n)) : 0.f;
+    // decay exp(dt * A) = 2^(dt * A * log2 e), A = -exp(A_log)
+    A[i] = ok ? -expf(ld(static_cast<const T*>(p.A_log) + static_cast<int64_t>(c) * N + n)) * 1.4426950408889634f : 0.f;
     S[i] = ok ? st_row[n] : 0.f;
   }
   const float Dc = live ? ld(static_cast<const T*>(p.D) + c) : 0.f;
@@ -333,14 +519,15 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelScanArgs
     __syncthreads();
     for (int i = threadIdx.x; i < nt * kSelCh; i += kSelThreads) {
       const int tt = i / kSelCh, cc = i % kSelCh;
-      float dtv = 0.f, xv = 0.f;
+      float dtv = 0.f, xv = 0.f, zg = p.out_scale;
       if (c0 + cc < p.C) {
+        if (z != nullptr) { const float zv = ld(z + static_cast<int64_t>(t0 + tt) * p.ldz + c0 + cc); zg *= zv * sigmoidf_(zv); }
         const float pre = p.dt_pre[static_cast<int64_t>(t0 + tt) * p.lddt + c0 + cc] +
                           (p.dt_bias != nullptr ? ld(static_cast<const T*>(p.dt_bias) + c0 + cc) : 0.f);
         dtv = pre > 20.f ? pre : log1pf(expf(pre));
         xv = ld(x + static_cast<int64_t>(t0 + tt) * p.ldx + c0 + cc);
       }
-      sdt[i] = dtv; sx[i] = xv;
+      sdt[i] = dtv; sx[i] = xv; sz[i] = zg;
     }
     for (int i = threadIdx.x; i < nt * N; i += kSelThreads) {
       const int tt = i / N, n = i % N;
@@ -356,18 +543,18 @@ __global__ void __launch_bounds__(kSelThreads) selective_scan_kernel(SelScanArgs
       for (int i = 0; i < NS; ++i) {
         const int n = part + kSelParts * i;
         if (n < N) {
-          S[i] = fmaf(expf(dtv * A[i]), S[i], dx * sB[tt * N + n]);
+          S[i] = fmaf(exp2f(dtv * A[i]), S[i], dx * sB[tt * N + n]);
           acc = fmaf(S[i], sC[tt * N + n], acc);
         }
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
       acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      if (live && part == 0) {
-        const int64_t t = t0 + tt;
-        float v = fmaf(Dc, xv, acc);
-        if (z != nullptr) { const float zv = ld(z + t * p.ldz + c); v *= zv * sigmoidf_(zv); }
-        st(y + t * p.ldy + c, v * p.out_scale);
-      }
+      if (part == 0) sy[tt * kSelCh + cl] = fmaf(Dc, xv, acc) * sz[tt * kSelCh + cl];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * kSelCh; i += kSelThreads) {
+      const int tt = i / kSelCh, cc = i % kSelCh;
+      if (c0 + cc < p.C) st(y + static_cast<int64_t>(t0 + tt) * p.ldy + c0 + cc, sy[i]);
     }
   }
 #pragma unroll
@@ -387,11 +574,28 @@ bool stream_mix_norm(const StreamNormArgs& p, int n_tok, bool bf16, cudaStream_t
   if (n_tok == 0) return true;
   const size_t smem = p.inp != nullptr ? static_cast<size_t>(p.W) * sizeof(float) : 0;
   if (smem > 200 * 1024) return false;
+  const size_t esz = bf16 ? 2 : 4;
+  auto al = [&](const void* q, size_t bytes) { return q == nullptr || reinterpret_cast<uintptr_t>(q) % bytes == 0; };
+  const bool vec = p.W % 4 == 0 && p.S <= 4 && al(p.x, 16) && al(p.a, 4 * esz) && al(p.b, 4 * esz) && al(p.bias_a, 4 * esz) &&
+                   al(p.ls, 4 * esz) && al(p.w, 4 * esz) && al(p.beta, 4 * esz) && al(p.h, 4 * esz) && p.lda % 4 == 0 && p.ldb % 4 == 0;
+#define SEQ_STREAM_VEC(SS)                                                                                                  \
+  {                                                                                                                         \
+    if (smem > 48 * 1024)                                                                                                   \
+      cudaFuncSetAttribute(stream_mix_norm_vec_kernel<T, SS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    stream_mix_norm_vec_kernel<T, SS><<<n_tok, 256, smem, s>>>(p);                                                          \
+  }
   SEQ_DISPATCH_T(bf16, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    stream_mix_norm_kernel<T><<<n_tok, 256, smem, s>>>(p);
+    if (vec && p.S == 1) SEQ_STREAM_VEC(1)
+    else if (vec && p.S == 2) SEQ_STREAM_VEC(2)
+    else if (vec && p.S == 3) SEQ_STREAM_VEC(3)
+    else if (vec && p.S == 4) SEQ_STREAM_VEC(4)
+    else {
+      if (smem > 48 * 1024)
+        cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      stream_mix_norm_kernel<T><<<n_tok, 256, smem, s>>>(p);
+    }
   });
+#undef SEQ_STREAM_VEC
   return true;
 }
 
@@ -410,18 +614,39 @@ void head_rms_norm(const void* x, int64_t ldx, const void* w, void* y, int n_tok
                            static_cast<const T*>(x), ldx, static_cast<const T*>(w), static_cast<T*>(y), rows, heads, d, eps));
 }
 
+void window_attention_shape(int H, int G, int* QB, int* HC) {
+  const int rep = H / G;
+  *HC = std::min(rep, kWinWarps * kWinSlots);
+  *QB = std::max(1, (kWinWarps * kWinSlots) / *HC);
+}
+
+int window_attention_splits(int H, int G, int n_tok, int max_keys) {
+  int QB, HC;
+  window_attention_shape(H, G, &QB, &HC);
+  const int rep = H / G, ctas = n_tok * G * ((rep + HC - 1) / HC);
+  const int by_keys = (max_keys + 2 * kWinTile - 1) / (2 * kWinTile);     // at least two tiles per split
+  const int by_fill = (4 * 148 + ctas - 1) / ctas;
+  return std::max(1, std::min(std::min(by_keys, by_fill), 64));
+}
+
 template <typename T, int DVR>
 static bool launch_window(WindowAttnArgs& p, cudaStream_t s) {
   const int rep = p.H / p.G;
-  p.HC = std::min(rep, kWinWarps * kWinPairs);
-  p.QB = std::max(1, (kWinWarps * kWinPairs) / p.HC);
-  const size_t smem = (static_cast<size_t>(32) * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) + static_cast<size_t>(kWinTile) * p.dv +
-                       static_cast<size_t>(kWinWarps) * kWinPairs * kWinTile) * sizeof(float);
+  window_attention_shape(p.H, p.G, &p.QB, &p.HC);
+  if (p.n_splits > 1) p.QB = 1;
+  else p.n_splits = 1;
+  const size_t smem = (static_cast<size_t>(kWinWarps) * kWinSlots * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) +
+                       static_cast<size_t>(kWinTile) * p.dv + static_cast<size_t>(kWinWarps) * kWinSlots * kWinTile) * sizeof(float);
   if (smem > 220 * 1024) return false;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(window_attention_kernel<T, DVR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  dim3 grid((p.n_tok + p.QB - 1) / p.QB, p.G, (rep + p.HC - 1) / p.HC);
+  dim3 grid((p.n_tok + p.QB - 1) / p.QB, p.G, ((rep + p.HC - 1) / p.HC) * p.n_splits);
+  if (grid.z > 65535) return false;
   window_attention_kernel<T, DVR><<<grid, kWinWarps * 32, smem, s>>>(p);
+  if (p.n_splits > 1) {
+    const int64_t rows = static_cast<int64_t>(p.n_tok) * p.H;
+    window_attention_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(p);
+  }
   return true;
 }
 
@@ -429,6 +654,7 @@ bool window_attention_paged(const WindowAttnArgs& p_in, bool bf16, cudaStream_t 
   WindowAttnArgs p = p_in;
   if (p.n_tok == 0) return true;
   if (p.H % p.G != 0 || p.G > 65535) return false;
+  if (p.n_splits > 1 && p.ws == nullptr) return false;
   SEQ_DISPATCH_T(bf16, {
     if (p.dv <= 32) return launch_window<T, 1>(p, s);
     if (p.dv <= 64) return launch_window<T, 2>(p, s);
@@ -440,7 +666,7 @@ bool window_attention_paged(const WindowAttnArgs& p_in, bool bf16, cudaStream_t 
 
 template <typename T, int NS>
 static void launch_sel(const SelScanArgs& p, int R, cudaStream_t s) {
-  const size_t smem = (2 * static_cast<size_t>(kSelChunk) * kSelCh + 2 * static_cast<size_t>(kSelChunk) * p.N) * sizeof(float);
+  const size_t smem = (4 * static_cast<size_t>(kSelChunk) * kSelCh + 2 * static_cast<size_t>(kSelChunk) * p.N) * sizeof(float);
   dim3 grid((p.C + kSelCh - 1) / kSelCh, R);
   selective_scan_kernel<T, NS><<<grid, kSelThreads, smem, s>>>(p);
 }

@@ -263,7 +263,7 @@ class DynamicInferenceContext:
         vc[self._write_slots] = v
         self.kernel_calls += 1
         return seqmix.window_attention_paged(q, kc, vc, self._block_table, self._tok_req, self._tok_len, self.block_size, scale,
-                                             window, slopes, sink, gate, out_scale)
+                                             window, slopes, sink, gate, out_scale, self._max_len)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:

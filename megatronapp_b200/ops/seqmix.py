@@ -591,7 +591,7 @@ def head_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Te
 def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                            tok_req: torch.Tensor, tok_len: torch.Tensor, block_size: int, scale: float, window: int = 0,
                            slopes: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
-                           out_scale: float = 1.0) -> torch.Tensor:
+                           out_scale: float = 1.0, max_len: int = 0) -> torch.Tensor:
     """``q [T, H, d]`` against paged keys ``[slots, G, d]`` and values ``[slots, G, dv]``.  The token at position
     ``i = tok_len[t] - 1`` sees the keys ``j`` of its own sequence with ``0 <= i - j < window`` (``window = 0``: all up to
     ``i``)::
@@ -600,7 +600,8 @@ def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
 
     ``sink``: a key of score 0 without a value takes part in the normalisation.  ``gate [T, H]`` (pre-activation) multiplies
     head ``h``'s output by its sigmoid; ``out_scale`` multiplies everything.  Scores, weights and sums are fp32.  Returns
-    ``[T, H * dv]`` in ``q``'s dtype."""
+    ``[T, H * dv]`` in ``q``'s dtype.  ``max_len`` (the longest context, known to the host) lets a batch with one token per
+    sequence (``block_table`` has as many rows as ``q``) split its keys over several CTAs."""
     T, H, d = q.shape
     G, dv = kcache.shape[1], vcache.shape[2]
     if q.is_cuda:
@@ -609,7 +610,7 @@ def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         ext().window_attention_paged(_rows3(q), kcache, vcache, block_table, tok_req, tok_len,
                                      None if slopes is None else slopes.float().contiguous(),
                                      None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()), o,
-                                     int(block_size), float(scale), int(window), bool(sink), float(out_scale))
+                                     int(block_size), float(scale), int(window), bool(sink), float(out_scale), int(max_len))
         return o
     o = torch.empty(T, H, dv, dtype=torch.float32)
     req, lens = tok_req.tolist(), tok_len.tolist()

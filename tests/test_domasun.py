@@ -345,6 +345,42 @@ def test_attention_sees_one_marked_key_just_inside_the_window_and_not_outside(ct
     alone = seqmix.window_attention_paged(q[-1:].to(device), kc.to(device), vc.to(device), table, req[:1], lens[-1:], bs, 1.0, window,
                                           sl.to(device), True)
     close(alone[0].view(H, dd), want, 1e-5)
+    # a decoding batch (one token per sequence, the longest context known): the keys are split over several CTAs on the GPU
+    split = seqmix.window_attention_paged(q[-1:].to(device), kc.to(device), vc.to(device), table, req[:1], lens[-1:], bs, 1.0, window,
+                                          sl.to(device), True, max_len=ctx_len)
+    close(split[0].view(H, dd), want, 1e-5)
+
+
+@pytest.mark.parametrize("device", DEVICES)
+def test_decoding_batch_of_unequal_contexts_splits_keys_and_matches_prompts(device):
+    """Three sequences of different lengths decode one token each in one call (the split path on the GPU); every result
+    equals the last row of that sequence run as a prompt.  Gate, slopes, grouped heads."""
+    H, G, dd, bs, window = 6, 2, 16, 8, 70
+    lens = [3, 150, 517]
+    g = torch.Generator().manual_seed(0)
+    nb = [-(-n // bs) for n in lens]
+    perm = torch.randperm(sum(nb), generator=g)
+    table = torch.zeros(3, max(nb), dtype=torch.int32)
+    kc, vc = torch.zeros(sum(nb) * bs, G, dd), torch.zeros(sum(nb) * bs, G, dd)
+    qs, gates, wants, at = [], [], [], 0
+    slope = oracle.slopes(H)
+    for r, n in enumerate(lens):
+        table[r, :nb[r]] = perm[at:at + nb[r]].to(torch.int32)
+        at += nb[r]
+        k, v, q, gt = (torch.randn(n, G, dd, generator=g), torch.randn(n, G, dd, generator=g), torch.randn(1, H, dd, generator=g),
+                       torch.randn(1, H, generator=g))
+        pos = torch.arange(n)
+        slots = table[r].long()[pos // bs] * bs + pos % bs
+        kc[slots], vc[slots] = k, v
+        qs.append(q), gates.append(gt)
+        o = oracle.window_attention(q.double(), k.double(), v.double(), 0.25, window, slope, True, first=n - 1)[0]
+        wants.append(o * torch.sigmoid(gt[0].double()).unsqueeze(-1))
+    d = lambda t: t.to(device)  # noqa: E731
+    got = seqmix.window_attention_paged(d(torch.cat(qs)), d(kc), d(vc), d(table), d(torch.arange(3, dtype=torch.int32)),
+                                        d(torch.tensor(lens, dtype=torch.int32)), bs, 0.25, window, d(torch.tensor(slope)), True,
+                                        d(torch.cat(gates)), 1.0, max(lens))
+    for r in range(3):
+        close(got[r].view(H, dd), wants[r], 1e-5)
 
 
 @pytest.mark.parametrize("device", DEVICES)
