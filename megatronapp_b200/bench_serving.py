@@ -344,7 +344,7 @@ def kernel_numbers_domasun(s, device):
     slopes = distance_slopes(H).to(device)
     q, gate = rn(R, H, d, dtype=bf), rn(R, H, dtype=bf)
     bench("window_attention_paged.decode", lambda: seqmix.window_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, win, slopes,
-                                                                                 True, gate),
+                                                                                 True, gate, 1.0, L),
           R * win * G * d * 2 * 2, flops=R * win * H * d * 4, like="mixed_attention_paged.decode")
     talk = rn(H, H) * 0.3
     gate_m = rn(R, H * d, dtype=bf)

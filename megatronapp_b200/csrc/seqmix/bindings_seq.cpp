@@ -463,8 +463,9 @@ void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor&
   c10::cuda::CUDAGuard g(q.device());
   p.n_splits = 1;
   Tensor ws;
-  if (max_len > 0 && block_table.size(0) == q.size(0)) {     // one token per sequence: a decoding batch
-    const int keys = window > 0 ? static_cast<int>(std::min<int64_t>(window, max_len)) : static_cast<int>(max_len);
+  if (block_table.size(0) == q.size(0) && q.size(0) > 0) {   // one token per sequence: a decoding batch
+    const int64_t longest = max_len > 0 ? max_len : block_table.size(1) * block_size;      // unknown: what the tables can hold
+    const int keys = static_cast<int>(window > 0 ? std::min<int64_t>(window, longest) : longest);
     p.n_splits = b200seq::window_attention_splits(p.H, p.G, p.n_tok, keys);
     if (p.n_splits > 1) {
       ws = torch::empty({q.size(0), p.H, p.n_splits, p.dv + 2}, q.options().dtype(at::kFloat));

@@ -286,12 +286,12 @@ __device__ __forceinline__ void stage_tile<__nv_bfloat16>(float* dst, int ld_dst
   else stage_rows<__nv_bfloat16>(dst, ld_dst, cache, table, block_size, G, g, width, k0, n_keys);
 }
 
-template <typename T, int DVR>
-__global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(WindowAttnArgs p) {
+template <typename T, int DVR, int NW>
+__global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArgs p) {
   extern __shared__ __align__(16) float smem[];
   const int d = p.d, dv = p.dv, ldk = d + 1, ldv = dv;
   float* sq = smem;                                        // [warps][d][slots]
-  float* sk = sq + kWinWarps * kWinSlots * d;              // [tile][d + 1]
+  float* sk = sq + NW * kWinSlots * d;              // [tile][d + 1]
   float* sv = sk + kWinTile * ldk;                         // [tile][dv]
   float* sp = sv + kWinTile * ldv;                         // [warps][tile][slots]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
     int seg_end = seg + 1;
     while (seg_end < t1 && p.tok_req[seg_end] == r) ++seg_end;
     const int nq = seg_end - seg, n_pairs = nq * n_heads;
-    const int ns = warp < n_pairs ? (n_pairs - warp + kWinWarps - 1) / kWinWarps : 0;       // pairs of this warp
+    const int ns = warp < n_pairs ? (n_pairs - warp + NW - 1) / NW : 0;       // pairs of this warp
     const int* table = p.block_table + static_cast<int64_t>(r) * p.max_blocks;
     const int len_first = p.tok_len[seg], len_last = p.tok_len[seg_end - 1];
     int k_begin = p.window > 0 ? max(0, len_first - p.window) : 0, k_end = len_last;
@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
     __syncthreads();                                       // the previous segment's reads of sq are over
     for (int i = threadIdx.x; i < n_pairs * d; i += blockDim.x) {
       const int pr = i / d, c = i % d, qi = pr / n_heads, hh = pr % n_heads;
-      sq[((pr % kWinWarps) * d + c) * kWinSlots + pr / kWinWarps] =
+      sq[((pr % NW) * d + c) * kWinSlots + pr / NW] =
           ld(qbase + static_cast<int64_t>(seg + qi) * p.ldq + static_cast<int64_t>(g * rep + h_lo + hh) * d + c) * p.scale;
     }
     float m[kWinSlots], l[kWinSlots], acc[kWinSlots][DVR], slope[kWinSlots];
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
       for (int k = 0; k < DVR; ++k) acc[u][k] = 0.f;
       pos[u] = -1; lo[u] = 0; slope[u] = 0.f;
       if (u < ns) {
-        const int pr = warp + u * kWinWarps, qi = pr / n_heads, hh = pr % n_heads;
+        const int pr = warp + u * NW, qi = pr / n_heads, hh = pr % n_heads;
         pos[u] = p.tok_len[seg + qi] - 1;
         lo[u] = p.window > 0 ? max(0, pos[u] + 1 - p.window) : 0;
         slope[u] = p.slopes != nullptr ? p.slopes[g * rep + h_lo + hh] : 0.f;
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
 #pragma unroll
     for (int u = 0; u < kWinSlots; ++u) {
       if (u >= ns) continue;
-      const int pr = warp + u * kWinWarps, qi = pr / n_heads, hh = pr % n_heads, head = g * rep + h_lo + hh;
+      const int pr = warp + u * NW, qi = pr / n_heads, hh = pr % n_heads, head = g * rep + h_lo + hh;
       const int64_t t = seg + qi;
       if (p.n_splits > 1) {                                // (m, l, unnormalised sum) for the merge kernel
         float* w = p.ws + ((t * p.H + head) * p.n_splits + split) * (dv + 2);
@@ -625,7 +625,7 @@ int window_attention_splits(int H, int G, int n_tok, int max_keys) {
   window_attention_shape(H, G, &QB, &HC);
   const int rep = H / G, ctas = n_tok * G * ((rep + HC - 1) / HC);
   const int by_keys = (max_keys + 2 * kWinTile - 1) / (2 * kWinTile);     // at least two tiles per split
-  const int by_fill = (4 * 148 + ctas - 1) / ctas;
+  const int by_fill = (8 * 148 + ctas - 1) / ctas;
   return std::max(1, std::min(std::min(by_keys, by_fill), 64));
 }
 
@@ -635,14 +635,22 @@ static bool launch_window(WindowAttnArgs& p, cudaStream_t s) {
   window_attention_shape(p.H, p.G, &p.QB, &p.HC);
   if (p.n_splits > 1) p.QB = 1;
   else p.n_splits = 1;
-  const size_t smem = (static_cast<size_t>(kWinWarps) * kWinSlots * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) +
-                       static_cast<size_t>(kWinTile) * p.dv + static_cast<size_t>(kWinWarps) * kWinSlots * kWinTile) * sizeof(float);
+  // a decoding batch with few heads per kv head: four warps, one pair each, and more CTAs per SM
+  const int nw = (p.QB == 1 && p.HC <= 4) ? 4 : kWinWarps;
+  const size_t smem = (static_cast<size_t>(nw) * kWinSlots * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) +
+                       static_cast<size_t>(kWinTile) * p.dv + static_cast<size_t>(nw) * kWinSlots * kWinTile) * sizeof(float);
   if (smem > 220 * 1024) return false;
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(window_attention_kernel<T, DVR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   dim3 grid((p.n_tok + p.QB - 1) / p.QB, p.G, ((rep + p.HC - 1) / p.HC) * p.n_splits);
   if (grid.z > 65535) return false;
-  window_attention_kernel<T, DVR><<<grid, kWinWarps * 32, smem, s>>>(p);
+  if (nw == 4) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(window_attention_kernel<T, DVR, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    window_attention_kernel<T, DVR, 4><<<grid, 128, smem, s>>>(p);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(window_attention_kernel<T, DVR, kWinWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    window_attention_kernel<T, DVR, kWinWarps><<<grid, kWinWarps * 32, smem, s>>>(p);
+  }
   if (p.n_splits > 1) {
     const int64_t rows = static_cast<int64_t>(p.n_tok) * p.H;
     window_attention_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(p);
