@@ -74,7 +74,7 @@ template <> struct Wire<__nv_bfloat16> {
 // CTA c of the other ranks (tile-granular overlap, no grid-wide sync).
 //
 // Bandwidth: a thread that loads, scales and stores one float4 per iteration keeps ONE 16-byte request in flight, and
-// 32 CTAs x 512 threads x 16 B per ~1 us HBM round trip is ~0.25 TB/s -- what round 1 measured (219 GB/s).  Each thread
+// 32 CTAs x 512 threads x 16 B per ~1 us HBM round trip is ~0.25 TB/s -- a one-request version measured 219 GB/s.  Each thread
 // therefore issues kU independent loads before the first dependent store (phase 1) and the loads of all sources of kR
 // elements before the first add (phase 2): the NVLink stores are posted, so with 4-8 requests per thread in flight the
 // kernel is bound by the link, not by latency.
