@@ -464,6 +464,7 @@ void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor&
   p.n_splits = 1;
   Tensor ws;
   if (block_table.size(0) == q.size(0) && q.size(0) > 0) {   // one token per sequence: a decoding batch
+    p.decode = 1;
     const int64_t longest = max_len > 0 ? max_len : block_table.size(1) * block_size;      // unknown: what the tables can hold
     const int keys = static_cast<int>(window > 0 ? std::min<int64_t>(window, longest) : longest);
     p.n_splits = b200seq::window_attention_splits(p.H, p.G, p.n_tok, keys);

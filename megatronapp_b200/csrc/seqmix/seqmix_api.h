@@ -145,7 +145,8 @@ struct WindowAttnArgs {
   int n_tok, H, G, d, dv, block_size, max_blocks;
   int window;                     // 0: every earlier key is visible
   int sink;                       // 1: one is added to the softmax denominator
-  int n_splits;                   // > 1 (one token per sequence only): the visible keys are cut over that many CTAs
+  int decode;                     // 1: a decoding batch, one token per sequence
+  int n_splits;                   // > 1 (decode only): the visible keys are cut over that many CTAs
   float* ws;                      // [T, H, n_splits, dv + 2] when n_splits > 1
   int QB, HC;                     // filled by the launcher
   float scale, out_scale;

@@ -246,8 +246,7 @@ __global__ void __launch_bounds__(128) head_rms_norm_kernel(const T* __restrict_
 // the head dimension for all pairs of its warp at once (the queries of a warp lie pair-interleaved, so one 16-byte broadcast
 // read brings a channel of four pairs); the online softmax state (m, l) is kept per pair; values: a lane owns channels
 // lane, lane + 32, ... of the accumulators.  A block of tokens that straddles sequences walks them one after the other.
-// Decoding batches (one token per sequence) split the visible keys over several CTAs (n_splits), which leave (m, l, sum) in a
-// workspace for the merge kernel.
+// Decoding batches (one token per sequence) run window_attention_decode_kernel below.
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kWinWarps = 8, kWinSlots = 8, kWinTile = 32;
 
@@ -286,8 +285,9 @@ __device__ __forceinline__ void stage_tile<__nv_bfloat16>(float* dst, int ld_dst
   else stage_rows<__nv_bfloat16>(dst, ld_dst, cache, table, block_size, G, g, width, k0, n_keys);
 }
 
-template <typename T, int DVR, int NW>
-__global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArgs p) {
+template <typename T, int DVR>
+__global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(WindowAttnArgs p) {
+  constexpr int NW = kWinWarps;
   extern __shared__ __align__(16) float smem[];
   const int d = p.d, dv = p.dv, ldk = d + 1, ldv = dv;
   float* sq = smem;                                        // [warps][d][slots]
@@ -296,8 +296,7 @@ __global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArg
   float* sp = sv + kWinTile * ldv;                         // [warps][tile][slots]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y, rep = p.H / p.G;
-  const int chunk = blockIdx.z / p.n_splits, split = blockIdx.z % p.n_splits;
-  const int h_lo = chunk * p.HC, n_heads = min(p.HC, rep - h_lo);          // heads of this chunk, relative to the group
+  const int h_lo = blockIdx.z * p.HC, n_heads = min(p.HC, rep - h_lo);     // heads of this chunk, relative to the group
   const int t0 = blockIdx.x * p.QB, t1 = min(p.n_tok, t0 + p.QB);
   const T* qbase = static_cast<const T*>(p.q);
   const T* kc = static_cast<const T*>(p.kcache);
@@ -315,12 +314,7 @@ __global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArg
     const int ns = warp < n_pairs ? (n_pairs - warp + NW - 1) / NW : 0;       // pairs of this warp
     const int* table = p.block_table + static_cast<int64_t>(r) * p.max_blocks;
     const int len_first = p.tok_len[seg], len_last = p.tok_len[seg_end - 1];
-    int k_begin = p.window > 0 ? max(0, len_first - p.window) : 0, k_end = len_last;
-    if (p.n_splits > 1) {                                  // one query per CTA: its keys are cut into n_splits runs of whole tiles
-      const int per = ((k_end - k_begin + p.n_splits - 1) / p.n_splits + kWinTile - 1) / kWinTile * kWinTile;
-      k_begin += split * per;
-      k_end = min(k_end, k_begin + per);
-    }
+    const int k_begin = p.window > 0 ? max(0, len_first - p.window) : 0, k_end = len_last;
     __syncthreads();                                       // the previous segment's reads of sq are over
     for (int i = threadIdx.x; i < n_pairs * d; i += blockDim.x) {
       const int pr = i / d, c = i % d, qi = pr / n_heads, hh = pr % n_heads;
@@ -329,7 +323,7 @@ __global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArg
     }
     float m[kWinSlots], l[kWinSlots], acc[kWinSlots][DVR], slope[kWinSlots];
     int pos[kWinSlots], lo[kWinSlots];
-    const bool with_sink = p.sink && split == 0;
+    const bool with_sink = p.sink != 0;
 #pragma unroll
     for (int u = 0; u < kWinSlots; ++u) {
       m[u] = with_sink ? 0.f : -INFINITY;
@@ -424,16 +418,6 @@ __global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArg
       if (u >= ns) continue;
       const int pr = warp + u * NW, qi = pr / n_heads, hh = pr % n_heads, head = g * rep + h_lo + hh;
       const int64_t t = seg + qi;
-      if (p.n_splits > 1) {                                // (m, l, unnormalised sum) for the merge kernel
-        float* w = p.ws + ((t * p.H + head) * p.n_splits + split) * (dv + 2);
-        if (lane == 0) { w[0] = m[u]; w[1] = l[u]; }
-#pragma unroll
-        for (int k = 0; k < DVR; ++k) {
-          const int c = lane + 32 * k;
-          if (c < dv) w[2 + c] = acc[u][k];
-        }
-        continue;
-      }
       float f = p.out_scale / (l[u] > 0.f ? l[u] : 1.f);
       if (gate != nullptr) f *= sigmoidf_(ld(gate + t * p.ldg + head));
 #pragma unroll
@@ -446,6 +430,248 @@ __global__ void __launch_bounds__(NW * 32) window_attention_kernel(WindowAttnArg
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same attention for a decoding batch (one token per sequence).  grid (tokens, kv heads, head chunks x key splits), four
+// warps.  All (at most NP) heads of the chunk share the token, so every warp carries all of them and the warps divide the KEYS:
+// of a staged tile of 32 keys warp w owns keys 8 w .. 8 w + 7.  Scores: lane = (key, quarter); a lane walks channels
+// quarter, quarter + 4, ... of its key for all heads at once (queries head-interleaved: one vector read per channel), and
+// two shuffles add the quarters.  Each warp keeps an online softmax state (m, l, sum) over its own keys; values: a lane
+// owns channels lane, lane + 32, ... for all heads.  The four states are merged through shared memory at the end, and go
+// to the output or, with key splits, to the workspace of the merge kernel.  The page slots of a tile are looked up one tile
+// ahead by 32 threads, so that staging has no divisions.
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int kDecWarps = 4, kDecKeys = kWinTile / kDecWarps;
+
+template <typename T> struct StageVec;
+template <> struct StageVec<float> {
+  static constexpr int kN = 4;
+  using Raw = float4;
+  static __device__ __forceinline__ Raw fetch(const float* src) { return *reinterpret_cast<const float4*>(src); }
+  static __device__ __forceinline__ void put(float* o, const Raw& r) { *reinterpret_cast<float4*>(o) = r; }
+};
+template <> struct StageVec<__nv_bfloat16> {
+  static constexpr int kN = 8;
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw fetch(const __nv_bfloat16* src) { return *reinterpret_cast<const uint4*>(src); }
+  static __device__ __forceinline__ void put(float* o, const Raw& r) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+    const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]), c = __bfloat1622float2(h2[2]), e = __bfloat1622float2(h2[3]);
+    *reinterpret_cast<float4*>(o) = make_float4(a.x, a.y, b.x, b.y);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(c.x, c.y, e.x, e.y);
+  }
+};
+// Rows of `width` values at the cached slots `slots[j]`, of one or two caches of equal width, -> dst[j][ld] as fp32 (ld a
+// multiple of 4).  Loads go out in batches of kStageBatch per cache before the first dependent store.
+constexpr int kStageBatch = 4;
+template <typename T, bool kTwo>
+__device__ __forceinline__ void stage_slots(float* dst_a, int ld_a, const T* cache_a, float* dst_b, int ld_b, const T* cache_b,
+                                            const int64_t* slots, int G, int g, int width, int n_keys) {
+  constexpr int V = StageVec<T>::kN;
+  using Raw = typename StageVec<T>::Raw;
+  if (width % V == 0) {
+    const int per_row = width / V, total = n_keys * per_row;
+    const int sh = (per_row & (per_row - 1)) == 0 ? __ffs(per_row) - 1 : -1;
+    for (int i0 = threadIdx.x; i0 < total; i0 += kStageBatch * blockDim.x) {
+      Raw ra[kStageBatch], rb[kStageBatch];
+      int off_a[kStageBatch], off_b[kStageBatch];
+#pragma unroll
+      for (int e = 0; e < kStageBatch; ++e) {
+        const int i = i0 + e * blockDim.x;
+        off_a[e] = -1;
+        if (i < total) {
+          const int j = sh >= 0 ? i >> sh : i / per_row, c = (i - j * per_row) * V;
+          const int64_t src = (slots[j] * G + g) * width + c;
+          ra[e] = StageVec<T>::fetch(cache_a + src);
+          if (kTwo) rb[e] = StageVec<T>::fetch(cache_b + src);
+          off_a[e] = j * ld_a + c;
+          off_b[e] = j * ld_b + c;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < kStageBatch; ++e) {
+        if (off_a[e] >= 0) {
+          StageVec<T>::put(dst_a + off_a[e], ra[e]);
+          if (kTwo) StageVec<T>::put(dst_b + off_b[e], rb[e]);
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n_keys * width; i += blockDim.x) {
+      const int j = i / width, c = i - j * width;
+      const int64_t src = (slots[j] * G + g) * width + c;
+      dst_a[j * ld_a + c] = ld(cache_a + src);
+      if (kTwo) dst_b[j * ld_b + c] = ld(cache_b + src);
+    }
+  }
+}
+
+template <typename T, int DVR, int NP>
+__global__ void __launch_bounds__(kDecWarps * 32, 4) window_attention_decode_kernel(WindowAttnArgs p) {
+  extern __shared__ __align__(16) float smem[];
+  const int d = p.d, dv = p.dv;
+  const int dq = (d + 3) / 4 * 4, ldk = dq + 4, ldv = (dv + 3) / 4 * 4;   // ldk = 4 mod 32 for d a multiple of 32: no bank conflicts
+  float* sq = smem;                                        // [d][NP]
+  float* sk = sq + dq * NP;                                // [tile][ldk]
+  float* sv = sk + kWinTile * ldk;                         // [tile][ldv]
+  int64_t* sslot = reinterpret_cast<int64_t*>(sv + kWinTile * ldv);       // [2][tile]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, kl = lane >> 2, part = lane & 3;
+  const int t = blockIdx.x, g = blockIdx.y, rep = p.H / p.G;
+  const int chunk = blockIdx.z / p.n_splits, split = blockIdx.z % p.n_splits;
+  const int h_lo = chunk * p.HC, n_heads = min(p.HC, rep - h_lo);
+  const T* kc = static_cast<const T*>(p.kcache);
+  const T* vc = static_cast<const T*>(p.vcache);
+  const int* table = p.block_table + static_cast<int64_t>(p.tok_req[t]) * p.max_blocks;
+  const int pos = p.tok_len[t] - 1;
+  const int lo = p.window > 0 ? max(0, pos + 1 - p.window) : 0;
+  int k_begin = lo, k_end = pos + 1;
+  if (p.n_splits > 1) {                                    // the visible keys are cut into n_splits runs of whole tiles
+    const int per = ((k_end - k_begin + p.n_splits - 1) / p.n_splits + kWinTile - 1) / kWinTile * kWinTile;
+    k_begin += split * per;
+    k_end = min(k_end, k_begin + per);
+  }
+  const T* qrow = static_cast<const T*>(p.q) + static_cast<int64_t>(t) * p.ldq + static_cast<int64_t>(g * rep + h_lo) * d;
+  for (int i = threadIdx.x; i < d * NP; i += blockDim.x) {
+    const int c = i / NP, u = i % NP;
+    sq[i] = u < n_heads ? ld(qrow + u * d + c) * p.scale : 0.f;
+  }
+  auto slot_of = [&](int key) {
+    return static_cast<int64_t>(table[key / p.block_size]) * p.block_size + key % p.block_size;
+  };
+  if (threadIdx.x < kWinTile && k_begin + static_cast<int>(threadIdx.x) < k_end) sslot[threadIdx.x] = slot_of(k_begin + threadIdx.x);
+
+  float m[NP], l[NP], slope[NP], acc[NP][DVR];
+  const bool with_sink = p.sink && split == 0 && warp == 0;
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+    m[u] = with_sink ? 0.f : -INFINITY;
+    l[u] = with_sink ? 1.f : 0.f;
+    slope[u] = (p.slopes != nullptr && u < n_heads) ? p.slopes[g * rep + h_lo + u] : 0.f;
+#pragma unroll
+    for (int k = 0; k < DVR; ++k) acc[u][k] = 0.f;
+  }
+  int it = 0;
+  for (int k0 = k_begin; k0 < k_end; k0 += kWinTile, ++it) {
+    const int n_keys = min(kWinTile, k_end - k0);
+    __syncthreads();                                       // the previous tile is used up; sq and this tile's slots are written
+    const int64_t* slots = sslot + (it & 1) * kWinTile;
+    if (threadIdx.x < kWinTile && k0 + kWinTile + static_cast<int>(threadIdx.x) < k_end)
+      sslot[((it + 1) & 1) * kWinTile + threadIdx.x] = slot_of(k0 + kWinTile + threadIdx.x);
+    if (d == dv) {
+      stage_slots<T, true>(sk, ldk, kc, sv, ldv, vc, slots, p.G, g, d, n_keys);
+    } else {
+      stage_slots<T, false>(sk, ldk, kc, nullptr, 0, nullptr, slots, p.G, g, d, n_keys);
+      stage_slots<T, false>(sv, ldv, vc, nullptr, 0, nullptr, slots, p.G, g, dv, n_keys);
+    }
+    __syncthreads();
+    const int row0 = warp * kDecKeys;
+    if (row0 >= n_keys) continue;                          // none of this warp's keys in the last tile
+    const int row = row0 + kl, key = k0 + row;
+    const bool vis = row < n_keys;                         // k_begin >= lo and k_end <= pos + 1: every staged key is visible
+    float s[NP];
+#pragma unroll
+    for (int u = 0; u < NP; ++u) s[u] = 0.f;
+    if (vis) {
+      const float* krow = sk + row * ldk;
+      for (int c = part; c < d; c += 4) {
+        const float kv = krow[c];
+        const float* qc = sq + c * NP;
+        if constexpr (NP % 4 == 0) {
+#pragma unroll
+          for (int v = 0; v < NP / 4; ++v) {
+            const float4 qa = *reinterpret_cast<const float4*>(qc + 4 * v);
+            s[4 * v] = fmaf(qa.x, kv, s[4 * v]); s[4 * v + 1] = fmaf(qa.y, kv, s[4 * v + 1]);
+            s[4 * v + 2] = fmaf(qa.z, kv, s[4 * v + 2]); s[4 * v + 3] = fmaf(qa.w, kv, s[4 * v + 3]);
+          }
+        } else if constexpr (NP == 2) {
+          const float2 qa = *reinterpret_cast<const float2*>(qc);
+          s[0] = fmaf(qa.x, kv, s[0]); s[1] = fmaf(qa.y, kv, s[1]);
+        } else {
+          s[0] = fmaf(qc[0], kv, s[0]);
+        }
+      }
+    }
+    float pw[NP];
+    const float dist = static_cast<float>(pos - key);
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      pw[u] = 0.f;
+      if (u < n_heads) {
+        float su = s[u];
+        su += __shfl_xor_sync(0xffffffffu, su, 1);
+        su += __shfl_xor_sync(0xffffffffu, su, 2);
+        const float sc = vis ? su - slope[u] * dist : -INFINITY;
+        const float m_new = fmaxf(m[u], warp_max(sc));     // finite: the warp's first key is visible
+        pw[u] = vis ? expf(sc - m_new) : 0.f;
+        const float corr = expf(m[u] - m_new);             // m = -inf: 0, and l and acc are 0 then
+        l[u] = l[u] * corr + warp_sum(part == 0 ? pw[u] : 0.f);
+        m[u] = m_new;
+#pragma unroll
+        for (int k = 0; k < DVR; ++k) acc[u][k] *= corr;
+      }
+    }
+    const int mine = min(kDecKeys, n_keys - row0);
+    for (int jj = 0; jj < mine; ++jj) {
+      float pj[NP];
+#pragma unroll
+      for (int u = 0; u < NP; ++u) pj[u] = __shfl_sync(0xffffffffu, pw[u], jj * 4);
+      const float* vrow = sv + (row0 + jj) * ldv;
+#pragma unroll
+      for (int k = 0; k < DVR; ++k) {
+        const int c = lane + 32 * k;
+        if (c < dv) {
+          const float vv = vrow[c];
+#pragma unroll
+          for (int u = 0; u < NP; ++u) acc[u][k] = fmaf(pj[u], vv, acc[u][k]);
+        }
+      }
+    }
+  }
+  // merge the four warps' states: [warp][head][m, l, sum(dv)] over the tile buffers
+  __syncthreads();
+  float* sm = sk;
+  const int ldm = dv + 2;
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+    if (u >= n_heads) continue;
+    float* w = sm + (warp * NP + u) * ldm;
+    if (lane == 0) { w[0] = m[u]; w[1] = l[u]; }
+#pragma unroll
+    for (int k = 0; k < DVR; ++k) {
+      const int c = lane + 32 * k;
+      if (c < dv) w[2 + c] = acc[u][k];
+    }
+  }
+  __syncthreads();
+  for (int u = warp; u < n_heads; u += kDecWarps) {
+    float M = -INFINITY, f[kDecWarps], L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) M = fmaxf(M, sm[(w * NP + u) * ldm]);
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) {
+      const float mw = sm[(w * NP + u) * ldm];
+      f[w] = (mw != -INFINITY) ? expf(mw - M) : 0.f;
+      L = fmaf(sm[(w * NP + u) * ldm + 1], f[w], L);
+    }
+    const int head = g * rep + h_lo + u;
+    const int64_t orow = static_cast<int64_t>(t) * p.H + head;
+    float* wsrow = p.n_splits > 1 ? p.ws + (orow * p.n_splits + split) * ldm : nullptr;
+    float fo = 0.f;
+    if (wsrow != nullptr) {
+      if (lane == 0) { wsrow[0] = M; wsrow[1] = L; }
+    } else {
+      fo = p.out_scale / (L > 0.f ? L : 1.f);
+      if (p.gate != nullptr) fo *= sigmoidf_(ld(static_cast<const T*>(p.gate) + static_cast<int64_t>(t) * p.ldg + head));
+    }
+    for (int c = lane; c < dv; c += 32) {
+      float a = 0.f;
+#pragma unroll
+      for (int w = 0; w < kDecWarps; ++w) a = fmaf(sm[(w * NP + u) * ldm + 2 + c], f[w], a);
+      if (wsrow != nullptr) wsrow[2 + c] = a;
+      else st(static_cast<T*>(p.out) + orow * dv + c, a * fo);
+    }
+  }
+}
+
 // one warp per (token, head): the partial results of the key splits become the head's output
 template <typename T>
 __global__ void __launch_bounds__(128) window_attention_merge_kernel(WindowAttnArgs p) {
@@ -454,23 +680,25 @@ __global__ void __launch_bounds__(128) window_attention_merge_kernel(WindowAttnA
   const int lane = threadIdx.x & 31, dv = p.dv;
   const int64_t t = row / p.H;
   const int head = static_cast<int>(row % p.H);
-  const float* w = p.ws + row * p.n_splits * (dv + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, w[s * (dv + 2)]);
-  float L = 0.f;
-  for (int s = 0; s < p.n_splits; ++s) {
-    const float ms = w[s * (dv + 2)];
-    if (ms != -INFINITY) L += w[s * (dv + 2) + 1] * expf(ms - M);
-  }
+  const int ldm = dv + 2;
+  const float* w = p.ws + row * p.n_splits * ldm;
+  // the weights of the (at most 64) splits: lane s holds those of splits s and s + 32
+  const bool has0 = lane < p.n_splits, has1 = lane + 32 < p.n_splits;
+  const float m0 = has0 ? w[lane * ldm] : -INFINITY, m1 = has1 ? w[(lane + 32) * ldm] : -INFINITY;
+  const float l0 = has0 ? w[lane * ldm + 1] : 0.f, l1 = has1 ? w[(lane + 32) * ldm + 1] : 0.f;
+  const float M = warp_max(fmaxf(m0, m1));
+  const float f0 = m0 != -INFINITY ? expf(m0 - M) : 0.f, f1 = m1 != -INFINITY ? expf(m1 - M) : 0.f;
+  const float L = warp_sum(l0 * f0 + l1 * f1);
   float f = p.out_scale / (L > 0.f ? L : 1.f);
   if (p.gate != nullptr) f *= sigmoidf_(ld(static_cast<const T*>(p.gate) + t * p.ldg + head));
-  for (int c = lane; c < dv; c += 32) {
+  for (int c0 = 0; c0 < dv; c0 += 32) {
+    const int c = c0 + lane;
     float a = 0.f;
     for (int s = 0; s < p.n_splits; ++s) {
-      const float ms = w[s * (dv + 2)];
-      if (ms != -INFINITY) a = fmaf(w[s * (dv + 2) + 2 + c], expf(ms - M), a);
+      const float fs = __shfl_sync(0xffffffffu, s < 32 ? f0 : f1, s & 31);
+      if (c < dv) a = fmaf(w[s * ldm + 2 + c], fs, a);
     }
-    st(static_cast<T*>(p.out) + row * dv + c, a * f);
+    if (c < dv) st(static_cast<T*>(p.out) + row * dv + c, a * f);
   }
 }
 
@@ -620,10 +848,11 @@ void window_attention_shape(int H, int G, int* QB, int* HC) {
   *QB = std::max(1, (kWinWarps * kWinSlots) / *HC);
 }
 
+constexpr int kDecMaxHeads = 8;                            // heads of one kv head that a decoding CTA carries
+
 int window_attention_splits(int H, int G, int n_tok, int max_keys) {
-  int QB, HC;
-  window_attention_shape(H, G, &QB, &HC);
-  const int rep = H / G, ctas = n_tok * G * ((rep + HC - 1) / HC);
+  const int rep = H / G, hc = std::min(rep, kDecMaxHeads);
+  const int ctas = n_tok * G * ((rep + hc - 1) / hc);
   const int by_keys = (max_keys + 2 * kWinTile - 1) / (2 * kWinTile);     // at least two tiles per split
   const int by_fill = (8 * 148 + ctas - 1) / ctas;
   return std::max(1, std::min(std::min(by_keys, by_fill), 64));
@@ -633,24 +862,33 @@ template <typename T, int DVR>
 static bool launch_window(WindowAttnArgs& p, cudaStream_t s) {
   const int rep = p.H / p.G;
   window_attention_shape(p.H, p.G, &p.QB, &p.HC);
-  if (p.n_splits > 1) p.QB = 1;
-  else p.n_splits = 1;
-  // a decoding batch with few heads per kv head: four warps, one pair each, and more CTAs per SM
-  const int nw = (p.QB == 1 && p.HC <= 4) ? 4 : kWinWarps;
-  const size_t smem = (static_cast<size_t>(nw) * kWinSlots * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) +
-                       static_cast<size_t>(kWinTile) * p.dv + static_cast<size_t>(nw) * kWinSlots * kWinTile) * sizeof(float);
+  p.n_splits = 1;
+  const size_t smem = (static_cast<size_t>(kWinWarps) * kWinSlots * p.d + static_cast<size_t>(kWinTile) * (p.d + 1) +
+                       static_cast<size_t>(kWinTile) * p.dv + static_cast<size_t>(kWinWarps) * kWinSlots * kWinTile) * sizeof(float);
   if (smem > 220 * 1024) return false;
-  dim3 grid((p.n_tok + p.QB - 1) / p.QB, p.G, ((rep + p.HC - 1) / p.HC) * p.n_splits);
+  dim3 grid((p.n_tok + p.QB - 1) / p.QB, p.G, (rep + p.HC - 1) / p.HC);
   if (grid.z > 65535) return false;
-  if (nw == 4) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(window_attention_kernel<T, DVR, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    window_attention_kernel<T, DVR, 4><<<grid, 128, smem, s>>>(p);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(window_attention_kernel<T, DVR, kWinWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    window_attention_kernel<T, DVR, kWinWarps><<<grid, kWinWarps * 32, smem, s>>>(p);
-  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(window_attention_kernel<T, DVR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  window_attention_kernel<T, DVR><<<grid, kWinWarps * 32, smem, s>>>(p);
+  return true;
+}
+
+template <typename T, int DVR, int NP>
+static bool launch_decode(WindowAttnArgs& p, cudaStream_t s) {
+  const int rep = p.H / p.G;
+  p.QB = 1;
+  p.HC = std::min(rep, NP);
+  if (p.n_splits < 1) p.n_splits = 1;
+  const int dq = (p.d + 3) / 4 * 4, ldv = (p.dv + 3) / 4 * 4;
+  const size_t smem = (static_cast<size_t>(dq) * NP + static_cast<size_t>(kWinTile) * (dq + 4) + static_cast<size_t>(kWinTile) * ldv) *
+                          sizeof(float) + 2 * kWinTile * sizeof(int64_t);
+  if (smem > 220 * 1024) return false;
+  dim3 grid(p.n_tok, p.G, ((rep + p.HC - 1) / p.HC) * p.n_splits);
+  if (grid.z > 65535) return false;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(window_attention_decode_kernel<T, DVR, NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  window_attention_decode_kernel<T, DVR, NP><<<grid, kDecWarps * 32, smem, s>>>(p);
   if (p.n_splits > 1) {
     const int64_t rows = static_cast<int64_t>(p.n_tok) * p.H;
     window_attention_merge_kernel<T><<<static_cast<unsigned>((rows + 3) / 4), 128, 0, s>>>(p);
@@ -658,11 +896,29 @@ static bool launch_window(WindowAttnArgs& p, cudaStream_t s) {
   return true;
 }
 
+template <typename T, int DVR>
+static bool launch_decode_heads(WindowAttnArgs& p, cudaStream_t s) {
+  const int rep = p.H / p.G;
+  if (rep == 1) return launch_decode<T, DVR, 1>(p, s);
+  if (rep == 2) return launch_decode<T, DVR, 2>(p, s);
+  if (rep <= 4) return launch_decode<T, DVR, 4>(p, s);
+  return launch_decode<T, DVR, kDecMaxHeads>(p, s);
+}
+
 bool window_attention_paged(const WindowAttnArgs& p_in, bool bf16, cudaStream_t s) {
   WindowAttnArgs p = p_in;
   if (p.n_tok == 0) return true;
   if (p.H % p.G != 0 || p.G > 65535) return false;
-  if (p.n_splits > 1 && p.ws == nullptr) return false;
+  if (p.n_splits > 1 && (p.ws == nullptr || !p.decode)) return false;
+  if (p.decode) {
+    SEQ_DISPATCH_T(bf16, {
+      if (p.dv <= 32) return launch_decode_heads<T, 1>(p, s);
+      if (p.dv <= 64) return launch_decode_heads<T, 2>(p, s);
+      if (p.dv <= 128) return launch_decode_heads<T, 4>(p, s);
+      if (p.dv <= 256) return launch_decode_heads<T, 8>(p, s);
+    });
+    return false;
+  }
   SEQ_DISPATCH_T(bf16, {
     if (p.dv <= 32) return launch_window<T, 1>(p, s);
     if (p.dv <= 64) return launch_window<T, 2>(p, s);

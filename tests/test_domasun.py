@@ -352,35 +352,40 @@ def test_attention_sees_one_marked_key_just_inside_the_window_and_not_outside(ct
 
 
 @pytest.mark.parametrize("device", DEVICES)
-def test_decoding_batch_of_unequal_contexts_splits_keys_and_matches_prompts(device):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("H,G,dd,dv,window,sink", [(6, 2, 16, 16, 70, True), (5, 5, 20, 20, 0, True), (4, 2, 32, 24, 33, False),
+                                                   (12, 1, 8, 40, 100, True), (8, 1, 64, 64, 500, True), (3, 1, 36, 36, 64, False)])
+def test_decoding_batch_of_unequal_contexts_splits_keys_and_matches_prompts(H, G, dd, dv, window, sink, dtype, device):
     """Three sequences of different lengths decode one token each in one call (the split path on the GPU); every result
-    equals the last row of that sequence run as a prompt.  Gate, slopes, grouped heads."""
-    H, G, dd, bs, window = 6, 2, 16, 8, 70
+    equals the last row of that sequence run as a prompt.  Gate, slopes; one, two, three, eight and twelve heads per kv head,
+    head sizes with and without 16-byte rows, values narrower and wider than keys, with and without window and sink."""
+    bs = 8
     lens = [3, 150, 517]
     g = torch.Generator().manual_seed(0)
     nb = [-(-n // bs) for n in lens]
     perm = torch.randperm(sum(nb), generator=g)
     table = torch.zeros(3, max(nb), dtype=torch.int32)
-    kc, vc = torch.zeros(sum(nb) * bs, G, dd), torch.zeros(sum(nb) * bs, G, dd)
+    kc, vc = torch.zeros(sum(nb) * bs, G, dd), torch.zeros(sum(nb) * bs, G, dv)
     qs, gates, wants, at = [], [], [], 0
     slope = oracle.slopes(H)
+    rnd = lambda *sh: torch.randn(*sh, generator=g).to(dtype).float()  # noqa: E731
     for r, n in enumerate(lens):
         table[r, :nb[r]] = perm[at:at + nb[r]].to(torch.int32)
         at += nb[r]
-        k, v, q, gt = (torch.randn(n, G, dd, generator=g), torch.randn(n, G, dd, generator=g), torch.randn(1, H, dd, generator=g),
-                       torch.randn(1, H, generator=g))
+        k, v, q, gt = rnd(n, G, dd), rnd(n, G, dv), rnd(1, H, dd), rnd(1, H)
         pos = torch.arange(n)
         slots = table[r].long()[pos // bs] * bs + pos % bs
         kc[slots], vc[slots] = k, v
         qs.append(q), gates.append(gt)
-        o = oracle.window_attention(q.double(), k.double(), v.double(), 0.25, window, slope, True, first=n - 1)[0]
+        o = oracle.window_attention(q.double(), k.double(), v.double(), 0.25, window, slope, sink, first=n - 1)[0]
         wants.append(o * torch.sigmoid(gt[0].double()).unsqueeze(-1))
     d = lambda t: t.to(device)  # noqa: E731
-    got = seqmix.window_attention_paged(d(torch.cat(qs)), d(kc), d(vc), d(table), d(torch.arange(3, dtype=torch.int32)),
-                                        d(torch.tensor(lens, dtype=torch.int32)), bs, 0.25, window, d(torch.tensor(slope)), True,
-                                        d(torch.cat(gates)), 1.0, max(lens))
+    da = lambda t: t.to(device, dtype)  # noqa: E731
+    got = seqmix.window_attention_paged(da(torch.cat(qs)), da(kc), da(vc), d(table), d(torch.arange(3, dtype=torch.int32)),
+                                        d(torch.tensor(lens, dtype=torch.int32)), bs, 0.25, window, d(torch.tensor(slope)), sink,
+                                        da(torch.cat(gates)), 1.0, max(lens))
     for r in range(3):
-        close(got[r].view(H, dd), wants[r], 1e-5)
+        close(got[r].view(H, dv).float(), wants[r], 1e-5 if dtype == torch.float32 else 8e-3)
 
 
 @pytest.mark.parametrize("device", DEVICES)
