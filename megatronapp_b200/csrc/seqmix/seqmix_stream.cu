@@ -39,7 +39,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {   // every thr
 // X_t <- sum_s mix[s, t] X_s + out[t] * y for all t at once.  Then, with `inp`: u = sum_s inp[s] X_s and
 // h = (u - mean) / sqrt(var + eps) * w + beta (or u / sqrt(mean(u^2) + eps) * w without beta).  One CTA per token.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256) stream_mix_norm_kernel(StreamNormArgs p) {

@@ -239,14 +239,15 @@ def test_unequal_batch_matches_each_alone_and_rows_are_reused(device):
 @pytest.mark.parametrize("device", DEVICES)
 def test_other_sizes_and_values_that_are_often_equal_or_one(device):
     """kv heads == heads, one kv head, one head, one expert, two taps, one tap, a state of one, rank one, a loop over
-    everything, a loop that runs once, no loop, scales of one, a window of one and a window longer than the prompt."""
+    everything, a loop that runs once, no loop, scales of one, a window of one and a window longer than the prompt, eleven streams."""
     left = {"heads": 1, "kv_heads": 1, "dim": 12, "vdim": 12, "scale": 1.0, "mask": {"size": 1}}
     right = {"inner": 6, "state": 1, "dt_rank": 1, "conv": 1}
     one = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}}
     moe1 = {"kind": "moe", "expert": {"ff": 4, "limit": 1.0}, "router": {"experts": 1, "top": 1}, "shared": {"ff": 4, "limit": 1.0}}
     for cfg in (config_of([layer(one, moe1), layer(PAR_C, MOE)], width=24, loop={"start": 0, "stop": 2, "times": 3}, streams=2),
                 config_of([layer(PAR_B, MOE_B), layer(one)], width=40, loop={"start": 1, "stop": 2, "times": 1}, streams=1, softcap=None),
-                config_of([layer(PAR_C, MOE_C)], width=16, eps=1e-3, streams=5)):
+                config_of([layer(PAR_C, MOE_C)], width=16, eps=1e-3, streams=5),
+                config_of([layer(PAR_B, MOE_B)], width=20, streams=11)):
         model, W = build(cfg, device, seed=11)
         toks = tokens_of(29, seed=8)
         close(run_cut(replayer(model), "a", toks, [13, 2, 9]), oracle.forward(cfg, W, toks), TOL[torch.float32])
