@@ -7,7 +7,7 @@ weights and a cache per pass; the logits are soft-capped.
 
 Assembled from the framework's parts: ``LanguageModelEmbedding`` (sinusoidal), ``StreamBlock`` of ``StreamLayer`` with
 ``SideBySideMixer(WindowAttention, SelectiveScanMixer)`` and ``MoELayer`` (``TopKRouter``, fused dispatcher, ``GroupedMLP``
-with ``ClampedGLU``, ``SharedExpertMLP``), a column-parallel output layer.  It follows the ``GPTModel`` call contract, so the
+with ``ClampedGLU``, ``SharedExpertMLP``), a column-parallel output layer.  It follows the ``GPTModel`` call signature, so the
 engines, the generation server and the trace replayer drive it like any other language model.
 """
 from __future__ import annotations

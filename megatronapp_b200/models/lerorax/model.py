@@ -5,7 +5,7 @@ and a clamped gated feed-forward.  A layer may run another layer's weights with 
 
 Assembled from the framework's parts: ``LanguageModelEmbedding`` + ``HashedBigramEmbedding``, ``OutputNormF32Block`` of
 ``OutputNormF32Layer`` with ``SideBySideMixer(MixedHeadAttention, GeneralizedDeltaMixer)`` or ``MinGRUMixer``, ``MLP`` with
-``ClampedGLU``, a column-parallel output layer.  It follows the ``GPTModel`` call contract, so the engines, the
+``ClampedGLU``, a column-parallel output layer.  It follows the ``GPTModel`` call signature, so the engines, the
 generation server and the trace replayer drive it like any other language model.
 """
 from __future__ import annotations

@@ -1,7 +1,7 @@
 """Model registry: the architecture name in a model folder's ``config.json`` picks the builder.
 
 A *model folder* holds ``config.json`` (with an ``architecture`` key) and optionally ``model.safetensors``.
-``build_model_from_dir`` returns an eval-mode model on ``device`` that follows the ``GPTModel`` call contract, ready for
+``build_model_from_dir`` returns an eval-mode model on ``device`` that follows the ``GPTModel`` call signature, ready for
 the inference engines.  New architectures register a builder ``f(path, params_dtype, device, **overrides) -> model``.
 """
 from __future__ import annotations

@@ -5,7 +5,7 @@ dense or mixture-of-experts squared-ReLU feed-forward, around an fp32 residual s
 The model is assembled from the framework's parts: ``LanguageModelEmbedding`` (scaled), ``ResidualF32Block`` of
 ``ResidualF32Layer`` with ``LatentSelfAttention`` / ``GatedDeltaMixer`` / ``MLSTMMixer``, ``MLP`` or ``MoELayer``
 (``TopKRouter`` with max-scored group-limited routing, all-gather dispatcher, grouped experts, shared expert), and a
-column-parallel output layer.  It follows the ``GPTModel`` call contract (``forward(input_ids, position_ids,
+column-parallel output layer.  It follows the ``GPTModel`` call signature (``forward(input_ids, position_ids,
 attention_mask, inference_context=...) -> [b, s, V]`` logits or the per-token loss when ``labels`` is given), so the
 engines, the generation server and the pipeline helpers drive it like any other language model.
 """

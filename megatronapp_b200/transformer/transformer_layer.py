@@ -139,7 +139,7 @@ class TransformerLayer(MegatronModule):
 
 
 class BaseTransformerLayer:
-    """Marker base class (reference ``BaseTransformerLayer``): layers implementing the ``TransformerLayer`` call contract --
+    """Marker base class (reference ``BaseTransformerLayer``): layers implementing the ``TransformerLayer`` call signature --
     ``forward(hidden_states, attention_mask, context, context_mask, rotary_pos_emb, inference_context, packed_seq_params)``
     returning ``(hidden_states, context)`` -- can be placed in a ``TransformerBlock`` spec."""
 
