@@ -198,6 +198,7 @@ class TransformerConfig(ModelParallelConfig):
     moe_router_score_function: str = "softmax"
     moe_router_dtype: Optional[str] = None
     moe_router_enable_expert_bias: bool = False
+    moe_router_logit_bias: bool = False        # a learned bias on the router logits
     moe_router_bias_update_rate: float = 1e-3
     moe_grouped_gemm: bool = False
     moe_use_legacy_grouped_gemm: bool = False

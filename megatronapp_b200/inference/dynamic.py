@@ -247,11 +247,11 @@ class DynamicInferenceContext:
 
     def attend_window(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
                       slopes: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
-                      out_scale: float = 1.0) -> torch.Tensor:
+                      out_scale: float = 1.0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Sliding-window grouped-query attention over the pages of cache ``layer``: ``q [T, H, d]``, new ``k [T, G, d]`` /
         ``v [T, G, dv]`` (written into their pages first; ``v`` may be a strided view), a distance penalty per head
-        (``slopes [H]``), an optional sink in the softmax denominator and a per-head output gate ``[T, H]`` (pre-activation)
-        -> ``[T, H * dv]``.  A token sees the ``window`` last positions of its sequence (0: all).  fp32 and 16-bit caches."""
+        (``slopes [H]``) or an additive bias by distance (``dist_bias [L, H]``), an optional sink in the softmax denominator
+        and a per-head output gate ``[T, H]`` (pre-activation) -> ``[T, H * dv]``.  A token sees the ``window`` last positions of its sequence (0: all).  fp32 and 16-bit caches."""
         from ..ops import seqmix
 
         if layer not in self.kv:
@@ -263,7 +263,7 @@ class DynamicInferenceContext:
         vc[self._write_slots] = v
         self.kernel_calls += 1
         return seqmix.window_attention_paged(q, kc, vc, self._block_table, self._tok_req, self._tok_len, self.block_size, scale,
-                                             window, slopes, sink, gate, out_scale, self._max_len)
+                                             window, slopes, sink, gate, out_scale, self._max_len, dist_bias)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:

@@ -139,6 +139,53 @@ class HashedBigramEmbedding(MegatronModule):
         return F.embedding(self.rows(ids, prev), self.weight).transpose(0, 1).contiguous()
 
 
+class PerLayerTokenEmbedding(MegatronModule):
+    """A second embedding table that gives every layer a small vector of its own for each token: row ``token`` of
+    ``weight [vocab, layers * dim]``, columns ``[i * dim, (i + 1) * dim)`` for layer ``i``.  ``forward`` looks the rows up once per
+    step, ``[T, layers * dim]`` (packed tokens); layers take their column slice (``TokenSideInput``)."""
+
+    def __init__(self, config, vocab_size: int, num_layers: int, dim: int):
+        super().__init__(config)
+        self.num_layers, self.dim = int(num_layers), int(dim)
+        dev = "cpu" if (config.use_cpu_initialization or not torch.cuda.is_available()) else torch.cuda.current_device()
+        self.weight = nn.Parameter(torch.zeros(vocab_size, self.num_layers * self.dim, dtype=config.params_dtype, device=dev))
+        if config.perform_initialization:
+            config.init_method(self.weight)
+
+    def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """``input_ids [b, s]`` -> ``[b * s, layers * dim]``, sequence after sequence (the packed order of the mixers)."""
+        return F.embedding(input_ids.long().reshape(-1), self.weight)
+
+    def layer_slice(self, rows: torch.Tensor, layer: int) -> torch.Tensor:
+        return rows[:, layer * self.dim:(layer + 1) * self.dim]
+
+
+class TokenSideInput(MegatronModule):
+    """A layer's input from ``PerLayerTokenEmbedding``: ``y = W_proj (gelu_tanh(W_gate x) * e)`` with ``x`` the residual stream
+    and ``e`` the token's vector for this layer.  The caller adds ``rms_norm(y) * norm_weight`` to the stream (a plain weight;
+    ``norms.OutputRMSNormAdd`` semantics, ``ops.seqmix.norm_add``)."""
+
+    def __init__(self, config, dim: int, eps: Optional[float] = None):
+        super().__init__(config)
+        from ...parallel.tp_layers import ColumnParallelLinear, RowParallelLinear
+
+        self.dim, self.eps = int(dim), config.layernorm_epsilon if eps is None else float(eps)
+        self.gate = ColumnParallelLinear(config.hidden_size, self.dim, config=config, init_method=config.init_method, bias=False,
+                                         skip_bias_add=False, gather_output=True)
+        self.proj = RowParallelLinear(self.dim, config.hidden_size, config=config, init_method=config.output_layer_init_method,
+                                      bias=False, input_is_parallel=False, skip_bias_add=True)
+        dev = self.gate.weight.device
+        self.norm_weight = nn.Parameter(torch.ones(config.hidden_size, dtype=config.params_dtype, device=dev))
+
+    def forward(self, x: torch.Tensor, e: torch.Tensor) -> torch.Tensor:
+        """``x [T, W]`` (the stream in the activation dtype), ``e [T, dim]`` -> ``y [T, W]`` before its norm."""
+        from ...ops import seqmix
+
+        g, _ = self.gate(x.unsqueeze(1))
+        y, _ = self.proj(seqmix.gelu_mul(g[:, 0], e.to(g.dtype)).unsqueeze(1))
+        return y[:, 0]
+
+
 def llama3_scaled_frequencies(dims: int, base: float, scaling: Optional[dict] = None) -> torch.Tensor:
     """Rotary frequencies ``base^(-2i / dims)``, ``i < dims / 2``, as fp32 (computed in fp64).  ``scaling`` (``factor``,
     ``low``, ``high``, ``original``) applies the wavelength-dependent rule of ``_apply_llama3_scaling``: short wavelengths

@@ -64,6 +64,13 @@ def _domasun(path, params_dtype, device, **overrides):
     return load_model_dir(path, params_dtype, device, **overrides)
 
 
+@register_architecture("Nunosun")
+def _nunosun(path, params_dtype, device, **overrides):
+    from .nunosun.loader import load_model_dir
+
+    return load_model_dir(path, params_dtype, device, **overrides)
+
+
 @register_architecture("GPTModel")
 def _gpt(path, params_dtype, device, **overrides):
     """A GPT / Llama-style folder: ``config.json`` holds ``TransformerConfig`` fields under ``transformer`` plus

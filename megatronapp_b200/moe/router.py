@@ -42,6 +42,9 @@ class TopKRouter(MegatronModule):
             config.init_method(self.weight)
         self.weight.data = self.weight.data.to(dtype=config.params_dtype)
         setattr(self.weight, "sequence_parallel", config.sequence_parallel)
+        # a learned bias added to the router logits (it takes part in the choice and in the weights)
+        self.logit_bias = nn.Parameter(torch.zeros(self.num_experts, dtype=config.params_dtype, device=dev)) \
+            if getattr(config, "moe_router_logit_bias", False) else None
         if config.moe_router_enable_expert_bias:
             self.register_buffer("local_tokens_per_expert", torch.zeros(self.num_experts, dtype=torch.float32, device=dev), persistent=False)
             self.register_buffer("expert_bias", torch.zeros(self.num_experts, dtype=torch.float32, device=dev))
@@ -55,7 +58,7 @@ class TopKRouter(MegatronModule):
     def gating(self, x):
         dt = torch.float32 if self.config.moe_router_dtype == "fp32" else (
             torch.float64 if self.config.moe_router_dtype == "fp64" else x.dtype)
-        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt))
+        return torch.nn.functional.linear(x.to(dt), self.weight.to(dt), None if self.logit_bias is None else self.logit_bias.to(dt))
 
     def apply_input_jitter(self, x):
         eps = self.config.moe_input_jitter_eps

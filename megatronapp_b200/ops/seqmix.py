@@ -111,22 +111,27 @@ def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.T
     return x, y.to(out_dtype)
 
 
-def gated_head_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], eps: float,
-                        out_dtype: torch.dtype) -> torch.Tensor:
+def gated_head_rms_norm(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], eps: float,
+                        out_dtype: torch.dtype, gate_act: str = "sigmoid") -> torch.Tensor:
     """``o`` fp32 ``[T, H, dv]``: every head divided by its own root mean square, times ``weight`` (``[dv]`` shared by
-    the heads, or ``[H * dv]``), times ``sigmoid(gate)`` (``[T, H * dv]`` pre-activation) -> ``[T, H * dv]``."""
+    the heads, or ``[H * dv]``; ``None``: no weight), times ``act(gate)`` (``[T, H * dv]`` pre-activation, any row stride;
+    ``gate_act`` is ``"sigmoid"`` or ``"silu"``) -> ``[T, H * dv]``."""
     T, H, dv = o.shape
+    if gate_act not in ("sigmoid", "silu"):
+        raise ValueError(f"unknown gate activation {gate_act!r}")
     if o.is_cuda:
         kernel_calls["gated_head_rms_norm"] += 1
         y = torch.empty(T, H * dv, dtype=out_dtype, device=o.device)
-        ext().gated_head_rms_norm(o.contiguous(), weight, None if gate is None else gate.contiguous(), y, float(eps))
+        ext().gated_head_rms_norm(o.contiguous(), weight, None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()),
+                                  y, float(eps), gate_act == "silu")
         return y
     y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
-    w = weight.float()
-    y = y * (w.view(1, 1, dv) if w.numel() == dv else w.view(1, H, dv))
+    if weight is not None:
+        w = weight.float()
+        y = y * (w.view(1, 1, dv) if w.numel() == dv else w.view(1, H, dv))
     y = y.reshape(T, H * dv)
     if gate is not None:
-        y = y * torch.sigmoid(gate.float())
+        y = y * (torch.sigmoid(gate.float()) if gate_act == "sigmoid" else F.silu(gate.float()))
     return y.to(out_dtype)
 
 
@@ -141,16 +146,16 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, win
 
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor, silu: bool = False,
-                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                bias: Optional[torch.Tensor] = None, residual: bool = False) -> torch.Tensor:
     """Depth-wise causal convolution over time, optionally followed by SiLU.  ``x [T, C]``, ``weight [C, taps]`` (last
     column multiplies the current token), ``bias [C]`` (optional), ``window [rows, taps - 1, C]``: the inputs that preceded
     each sequence's first token of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs
-    seen."""
+    seen.  ``residual``: the input itself is added to the result (``x + conv(x)``, after the activation if there is one)."""
     if x.is_cuda:
         kernel_calls["causal_conv_silu" if silu else "causal_conv"] += 1
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         ext().causal_conv(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), bias, pb.cu, pb.slots, pb.tok_seq,
-                          window, y, pb.max_len, bool(silu))
+                          window, y, pb.max_len, bool(silu), bool(residual))
         return y
     taps = weight.shape[1]
     w = weight.float()
@@ -163,7 +168,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: 
         y = sum(seq[j:j + (b - a)] * w[:, j] for j in range(taps))
         if bias is not None:
             y = y + bias.float()
-        out.append(F.silu(y) if silu else y)
+        y = F.silu(y) if silu else y
+        out.append(y + x[a:b].float() if residual else y)
         if taps > 1:
             window[s] = seq[-(taps - 1):].to(window.dtype)
     return torch.cat(out, dim=0).to(x.dtype)
@@ -176,8 +182,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: 
 def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, beta: torch.Tensor,
                     pb: PackedBatch, state: torch.Tensor, unit_eps: Optional[float] = 1e-6,
                     q_scale: float = 1.0) -> torch.Tensor:
-    """``q, k [T, KH, d]``, ``v [T, H, dv]``, ``log_decay [T, H, d]`` fp32 (<= 0), ``beta [T, H]`` fp32,
-    ``state [rows, H, d, dv]`` fp32 -> ``o [T, H, dv]`` fp32.  Per head, per token::
+    """``q, k [T, KH, d]``, ``v [T, H, dv]``, ``log_decay [T, H, d]`` (one decay per key channel) or ``[T, H]`` (one per
+    head) fp32 (<= 0), ``beta [T, H]`` fp32, ``state [rows, H, d, dv]`` fp32 -> ``o [T, H, dv]`` fp32.  Per head, per token::
 
         S <- exp(log_decay)[:, None] * S;  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
 
@@ -201,6 +207,8 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay
     if rep > 1:
         qf, kf = qf.repeat_interleave(rep, dim=1), kf.repeat_interleave(rep, dim=1)
     decay = torch.exp(log_decay.float())
+    if decay.dim() == 2:
+        decay = decay.unsqueeze(-1).expand(T, H, d)
     o = torch.empty(T, H, dv, dtype=torch.float32)
     for r in range(pb.num_seqs):
         a, b, s = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
@@ -327,23 +335,32 @@ def _rms(t: torch.Tensor, eps: float) -> torch.Tensor:
     return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
 
 
-def norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+def norm_add(x: torch.Tensor, a: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
              weight_offset: float = 0.0, b: Optional[torch.Tensor] = None, weight_a: Optional[torch.Tensor] = None,
-             weight_b: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``x`` fp32 ``[T, h]`` is updated in place by ``+ rms_norm(m) * (weight_offset + weight)`` and returned with a copy in
-    ``out_dtype``.  ``m`` is the sublayer output ``a``; with a second branch ``b`` it is the mean of the two branches, each
-    RMS-normed with its own plain weight: ``(rms_norm(a) * weight_a + rms_norm(b) * weight_b) / 2``."""
+             weight_b: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
+             next_weight: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x`` fp32 ``[T, h]`` is updated in place by ``+ rms_norm(m) * (weight_offset + weight) + extra`` and returned with
+    a second tensor in ``out_dtype``.  ``m`` is the sublayer output ``a``; with a second branch ``b`` it is the mean of the two
+    branches, each RMS-normed with its own plain weight: ``(rms_norm(a) * weight_a + rms_norm(b) * weight_b) / 2``.
+    ``weight = None``: ``m`` is added as it is, without the outer norm.  ``extra`` (optional) is another sublayer's output added
+    in the same pass.  The second tensor is the new ``x`` itself, or with ``next_weight`` its RMS norm times that weight (the
+    input of the sublayer that follows)."""
     if x.is_cuda:
         kernel_calls["norm_add"] += 1
         y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
         ext().norm_add(x, a.contiguous(), None if b is None else b.contiguous(), weight_a, weight_b, weight, y, float(eps),
-                       float(weight_offset))
+                       float(weight_offset), None if extra is None else extra.contiguous(), next_weight)
         return x, y
     m = a.float()
     if b is not None:
         m = 0.5 * (_rms(m, eps) * weight_a.float() + _rms(b.float(), eps) * weight_b.float())
-    x.add_(_rms(m, eps) * (weight.float() + weight_offset))
-    return x, x.to(out_dtype)
+    if weight is not None:
+        m = _rms(m, eps) * (weight.float() + weight_offset)
+    if extra is not None:
+        m = m + extra.float()
+    x.add_(m)
+    y = x if next_weight is None else _rms(x, eps) * next_weight.float()
+    return x, y.to(out_dtype)
 
 
 # ---------------------------------------------------------------------------
@@ -591,12 +608,15 @@ def head_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Te
 def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                            tok_req: torch.Tensor, tok_len: torch.Tensor, block_size: int, scale: float, window: int = 0,
                            slopes: Optional[torch.Tensor] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
-                           out_scale: float = 1.0, max_len: int = 0) -> torch.Tensor:
+                           out_scale: float = 1.0, max_len: int = 0, dist_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``q [T, H, d]`` against paged keys ``[slots, G, d]`` and values ``[slots, G, dv]``.  The token at position
     ``i = tok_len[t] - 1`` sees the keys ``j`` of its own sequence with ``0 <= i - j < window`` (``window = 0``: all up to
     ``i``)::
 
-        s_j = q . k_j * scale - slopes[h] * (i - j);     p_j = exp(s_j) / (sink + sum_j exp(s_j))
+        s_j = q . k_j * scale - slopes[h] * (i - j) + dist_bias[min(i - j, L - 1), h];   p_j = exp(s_j) / (sink + sum_j exp(s_j))
+
+    ``dist_bias`` (optional) is an fp32 table ``[L, H]`` of additive biases by distance; distances beyond its last row use the
+    last row.
 
     ``sink``: a key of score 0 without a value takes part in the normalisation.  ``gate [T, H]`` (pre-activation) multiplies
     head ``h``'s output by its sigmoid; ``out_scale`` multiplies everything.  Scores, weights and sums are fp32.  Returns
@@ -610,7 +630,8 @@ def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         ext().window_attention_paged(_rows3(q), kcache, vcache, block_table, tok_req, tok_len,
                                      None if slopes is None else slopes.float().contiguous(),
                                      None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()), o,
-                                     int(block_size), float(scale), int(window), bool(sink), float(out_scale), int(max_len))
+                                     int(block_size), float(scale), int(window), bool(sink), float(out_scale), int(max_len),
+                                     None if dist_bias is None else dist_bias.float().contiguous())
         return o
     o = torch.empty(T, H, dv, dtype=torch.float32)
     req, lens = tok_req.tolist(), tok_len.tolist()
@@ -631,6 +652,9 @@ def window_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.
         dist = qpos - pos.view(1, 1, -1)
         if slopes is not None:
             s = s - slopes.float().view(H, 1, 1) * dist
+        if dist_bias is not None:
+            idx = dist[0].clamp(0, dist_bias.shape[0] - 1)                              # [n, L]
+            s = s + dist_bias.float()[idx].permute(2, 0, 1)
         vis = (dist >= 0) & ((dist < window) if window > 0 else torch.ones_like(dist, dtype=torch.bool))
         s = s.masked_fill(~vis, float("-inf"))
         m = s.amax(-1, keepdim=True)
@@ -682,3 +706,91 @@ def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, B: torch.Tensor, C: to
     if z is not None:
         out = out * F.silu(z.float())
     return (out * out_scale).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------
+# retention: matrix memory with a fixed decay per head, no normaliser; rotary positions applied on the way in
+# ---------------------------------------------------------------------------
+
+def rotary_frequencies(rot_dims: int, base: float, device=None) -> Optional[torch.Tensor]:
+    """``base^(-2 i / rot_dims)`` for ``i = 0 .. rot_dims / 2 - 1`` (computed in fp64, returned as fp32); ``None`` when nothing rotates."""
+    if rot_dims <= 0:
+        return None
+    i = torch.arange(rot_dims // 2, dtype=torch.float64)
+    return torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims).float().to(device)
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, pb: PackedBatch, state: torch.Tensor,
+                   positions: Optional[torch.Tensor] = None, inv_freq: Optional[torch.Tensor] = None, k_scale: float = 1.0) -> torch.Tensor:
+    """``q, k [T, H, d]``, ``v [T, H, dv]``, ``decay [H]`` fp32, ``state [rows, H, d, dv]`` fp32 -> ``o [T, H, dv]`` fp32::
+
+        S <- decay_h * S + (k_scale * k) v^T;   o = S^T q
+
+    With ``inv_freq [n]`` (fp32) the first ``2 n`` dimensions of every q and k head are rotated first, dimension ``i`` paired
+    with ``i + n`` by the angle ``positions[t] * inv_freq[i]``: ``(u, w) -> (u cos - w sin, w cos + u sin)``.  Angles,
+    rotated vectors and the state are fp32."""
+    T, H, dv = v.shape
+    d = q.shape[2]
+    n_rot = 0 if inv_freq is None else int(inv_freq.numel())
+    if n_rot and positions is None:
+        raise ValueError("retention_scan: rotation needs positions")
+    if q.is_cuda:
+        kernel_calls["retention_scan"] += 1
+        o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+        ext().retention_scan(_rows3(q), _rows3(k), _rows3(v), decay.float().contiguous(),
+                             None if not n_rot else positions.contiguous().long(), None if not n_rot else inv_freq.float().contiguous(),
+                             pb.cu, pb.slots, state, o, float(k_scale), pb.max_len)
+        return o
+    qf, kf, vf = q.float().clone(), k.float().clone(), v.float()
+    if n_rot:
+        ang = positions.float().unsqueeze(-1) * inv_freq.float()                       # [T, n]
+        cs, sn = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+        for t in (qf, kf):
+            u, w = t[..., :n_rot].clone(), t[..., n_rot:2 * n_rot].clone()
+            t[..., :n_rot] = u * cs - w * sn
+            t[..., n_rot:2 * n_rot] = w * cs + u * sn
+    kf = kf * k_scale
+    dec = decay.float().view(H, 1, 1)
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    for r in range(pb.num_seqs):
+        a, b, s = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
+        S = state[s].clone()
+        for t in range(a, b):
+            S = dec * S + kf[t].unsqueeze(-1) * vf[t].unsqueeze(1)
+            o[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+        state[s] = S
+    return o
+
+
+# ---------------------------------------------------------------------------
+# polynomial activation of normalised powers
+# ---------------------------------------------------------------------------
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
+    """``z [..., F]``, ``coef [4] = (a, b, c, e)``: ``a N(z) + b N(z^2) + c N(z^3) + e`` with element-wise powers and ``N`` the
+    division of a row by its root mean square (``eps`` inside the root).  Statistics and the sum are fp32; the result
+    leaves in ``z``'s dtype."""
+    F_ = z.shape[-1]
+    if z.is_cuda:
+        kernel_calls["poly_norm"] += 1
+        z2 = z.reshape(-1, F_)
+        y = torch.empty(z2.shape[0], F_, dtype=z.dtype, device=z.device)
+        ext().poly_norm(z2 if z2.stride(1) == 1 else z2.contiguous(), coef.float().contiguous(), y, float(eps))
+        return y.view(z.shape)
+    zf, c = z.float(), coef.float()
+    return (c[0] * _rms(zf, eps) + c[1] * _rms(zf * zf, eps) + c[2] * _rms(zf * zf * zf, eps) + c[3]).to(z.dtype)
+
+
+# ---------------------------------------------------------------------------
+# tanh-GELU gate times a per-token vector
+# ---------------------------------------------------------------------------
+
+def gelu_mul(g: torch.Tensor, e: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(g) * e`` for ``g, e [T, n]`` (``e`` may be a column slice of a wider table), computed in fp32, in ``g``'s dtype;
+    ``gelu_tanh(z) = z / 2 * (1 + tanh(sqrt(2 / pi) * (z + 0.044715 z^3)))``."""
+    if g.is_cuda:
+        kernel_calls["gelu_mul"] += 1
+        y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
+        ext().gelu_mul(g if g.stride(1) == 1 else g.contiguous(), e if e.stride(1) == 1 else e.contiguous(), y)
+        return y
+    return (F.gelu(g.float(), approximate="tanh") * e.float()).to(g.dtype)

@@ -1,4 +1,4 @@
-"""Gated delta-rule mixer with one decay per head and key channel.
+"""Gated delta-rule mixer with one decay per head and key channel, or one per head.
 
 Per head a matrix memory ``S [d, dv]`` is carried from token to token::
 
@@ -9,6 +9,11 @@ with ``beta = sigmoid(W_b h)``.  q, k and v come out of a short causal depth-wis
 normalised to unit length head by head (q additionally times ``d^-1/2``).  The read-out is RMS-normalised per head with
 one weight vector common to all heads and gated by ``sigmoid(W_g2 W_g1 h)``.  Grouped heads: value head ``h`` uses q / k head
 ``h // (heads / kv_heads)``.
+
+Variants, all parameters: ``decay_per_head`` (``g`` is one value per head: ``W_a`` has ``heads`` rows and ``dt_bias`` ``heads``
+entries); ``decay_rank = 0`` / ``gate_rank = 0`` (the decay's / the gate's pre-activation comes straight out of the input
+projection, without the low-rank pair); ``gate_act = "silu"`` (the read-out is multiplied by ``silu`` of the gate instead of its
+sigmoid).
 
 The module keeps the framework's Mamba mixer shape (``ssm/mamba.py``): one fused input projection whose rows are the
 segments ``[q | k | v | a1 | g1 | b]``, one convolution over the ``[q | k | v]`` channels, state in the inference
@@ -37,25 +42,29 @@ def unpacked_tokens(t: torch.Tensor, s: int, b: int) -> torch.Tensor:
 
 class GatedDeltaMixer(MegatronModule):
     def __init__(self, config, layer_number: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int,
-                 conv_taps: int, decay_rank: int, gate_rank: int, eps: float = None, unit_eps: float = 1e-6):
+                 conv_taps: int, decay_rank: int, gate_rank: int, eps: float = None, unit_eps: float = 1e-6,
+                 decay_per_head: bool = False, gate_act: str = "sigmoid"):
         super().__init__(config)
         if num_heads % num_kv_heads:
             raise ValueError("gated delta: heads must be a multiple of kv_heads")
         self.layer_number = layer_number
         self.nh, self.nkv, self.d, self.dv, self.taps = num_heads, num_kv_heads, qk_dim, v_dim, conv_taps
-        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.decay_rank, self.gate_rank = int(decay_rank), int(gate_rank)
+        self.decay_per_head, self.gate_act = bool(decay_per_head), gate_act
         self.eps = config.layernorm_epsilon if eps is None else eps
         self.unit_eps = unit_eps
         self.qk_ch, self.v_ch = num_kv_heads * qk_dim, num_heads * v_dim
         self.conv_ch = 2 * self.qk_ch + self.v_ch
         col = dict(config=config, init_method=config.init_method, bias=False, skip_bias_add=False, gather_output=False)
-        self.in_proj = ColumnParallelLinear(config.hidden_size, self.conv_ch + decay_rank + gate_rank + num_heads, **col)
-        self.decay_up = ColumnParallelLinear(decay_rank, num_heads * qk_dim, **col)
-        self.gate_up = ColumnParallelLinear(gate_rank, self.v_ch, **col)
+        self.decay_ch = num_heads if self.decay_per_head else num_heads * qk_dim
+        self.a_rows, self.g_rows = self.decay_rank or self.decay_ch, self.gate_rank or self.v_ch
+        self.in_proj = ColumnParallelLinear(config.hidden_size, self.conv_ch + self.a_rows + self.g_rows + num_heads, **col)
+        self.decay_up = ColumnParallelLinear(decay_rank, self.decay_ch, **col) if self.decay_rank else None
+        self.gate_up = ColumnParallelLinear(gate_rank, self.v_ch, **col) if self.gate_rank else None
         dev, dt_ = self.in_proj.weight.device, config.params_dtype
         self.conv_weight = nn.Parameter(torch.randn(self.conv_ch, conv_taps, device=dev).mul_(conv_taps ** -0.5).to(dt_))
         self.A_log = nn.Parameter(torch.zeros(num_heads, device=dev, dtype=dt_))
-        self.dt_bias = nn.Parameter(torch.zeros(num_heads * qk_dim, device=dev, dtype=dt_))
+        self.dt_bias = nn.Parameter(torch.zeros(self.decay_ch, device=dev, dtype=dt_))
         self.norm_weight = nn.Parameter(torch.ones(v_dim, device=dev, dtype=dt_))
         self.out_proj = RowParallelLinear(self.v_ch, config.hidden_size, config=config,
                                           init_method=config.output_layer_init_method, bias=False, input_is_parallel=True,
@@ -64,22 +73,23 @@ class GatedDeltaMixer(MegatronModule):
             p._no_weight_decay = True
 
     def segments(self):
-        """Row counts of the ``[q | k | v | a1 | g1 | b]`` segments of ``in_proj``."""
-        return [("q", self.qk_ch), ("k", self.qk_ch), ("v", self.v_ch), ("a1", self.decay_rank), ("g1", self.gate_rank),
-                ("b", self.nh)]
+        """Row counts of the ``[q | k | v | a1 | g1 | b]`` segments of ``in_proj`` (``a1`` / ``g1`` are the full decay / gate rows
+        when their rank is 0)."""
+        return [("q", self.qk_ch), ("k", self.qk_ch), ("v", self.v_ch), ("a1", self.a_rows), ("g1", self.g_rows), ("b", self.nh)]
 
-    def forward(self, hidden_states, inference_context=None, **_):
+    def forward(self, hidden_states, inference_context=None, cache_index=None, **_):
         s, b = hidden_states.shape[0], hidden_states.shape[1]
+        key = self.layer_number if cache_index is None else cache_index
         proj, _ = self.in_proj(hidden_states)
         proj = packed_tokens(proj)                                                     # [T, ...]
-        qkv, a1, g1, braw = torch.split(proj, [self.conv_ch, self.decay_rank, self.gate_rank, self.nh], dim=-1)
+        qkv, a1, g1, braw = torch.split(proj, [self.conv_ch, self.a_rows, self.g_rows, self.nh], dim=-1)
         if inference_context is not None:
             if inference_context.is_static_batching():
                 raise NotImplementedError("recurrent mixers serve through the dynamic engine")
             pb = inference_context.packed
-            window = inference_context.recurrent_state(("delta.conv", self.layer_number), (self.taps - 1, self.conv_ch),
+            window = inference_context.recurrent_state(("delta.conv", key), (self.taps - 1, self.conv_ch),
                                                        proj.dtype)
-            state = inference_context.recurrent_state(("delta.S", self.layer_number), (self.nh, self.d, self.dv),
+            state = inference_context.recurrent_state(("delta.S", key), (self.nh, self.d, self.dv),
                                                       torch.float32)
         else:
             pb = seqmix.PackedBatch.dense(s, b, proj.device)
@@ -88,13 +98,16 @@ class GatedDeltaMixer(MegatronModule):
         qkv = seqmix.causal_conv_silu(qkv, self.conv_weight, pb, window)
         T = qkv.shape[0]
         q, k, v = torch.split(qkv, [self.qk_ch, self.qk_ch, self.v_ch], dim=-1)
-        dt, _ = self.decay_up(a1.contiguous())
-        log_decay = -torch.exp(self.A_log.float()).view(1, self.nh, 1) * F.softplus(
-            dt.float() + self.dt_bias.float()).view(T, self.nh, self.d)
+        dt = self.decay_up(a1.contiguous())[0] if self.decay_up is not None else a1
+        if self.decay_per_head:
+            log_decay = -torch.exp(self.A_log.float()) * F.softplus(dt.float() + self.dt_bias.float())          # [T, H]
+        else:
+            log_decay = -torch.exp(self.A_log.float()).view(1, self.nh, 1) * F.softplus(
+                dt.float() + self.dt_bias.float()).view(T, self.nh, self.d)
         beta = torch.sigmoid(braw.float())
         o = seqmix.delta_rule_scan(q.reshape(T, self.nkv, self.d), k.reshape(T, self.nkv, self.d),
                                    v.reshape(T, self.nh, self.dv), log_decay, beta, pb, state, self.unit_eps,
                                    self.d ** -0.5)
-        gate, _ = self.gate_up(g1.contiguous())
-        y = seqmix.gated_head_rms_norm(o, self.norm_weight, gate, self.eps, proj.dtype)
+        gate = self.gate_up(g1.contiguous())[0] if self.gate_up is not None else g1
+        y = seqmix.gated_head_rms_norm(o, self.norm_weight, gate, self.eps, proj.dtype, self.gate_act)
         return self.out_proj(unpacked_tokens(y, s, b))

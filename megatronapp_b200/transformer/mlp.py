@@ -146,6 +146,26 @@ class ClampedGLU:
         return hash((self.limit, self.alpha, self.shift))
 
 
+class PolyNorm(torch.nn.Module):
+    """Activation with four learned numbers ``coef = (a, b, c, e)``: ``a N(z) + b N(z^2) + c N(z^3) + e``, powers taken element
+    by element, ``N`` dividing a token's vector by its root mean square (``eps`` inside the root).  One sm_100a kernel
+    (``ops.seqmix.poly_norm``); statistics in fp32.  A module, since it owns weights: assign it to an ``MLP``'s
+    ``activation_func`` (built without a gate)."""
+
+    def __init__(self, config, eps: float = 1e-6):
+        super().__init__()
+        dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) else torch.cuda.current_device()
+        dtype = config.params_dtype if config is not None else torch.float32
+        self.eps = float(eps)
+        self.coef = torch.nn.Parameter(torch.tensor([1.0, 0.0, 0.0, 0.0], dtype=dtype, device=dev))
+        self.__name__ = "poly_norm"
+
+    def forward(self, x):
+        from ..ops import seqmix
+
+        return seqmix.poly_norm(x, self.coef, self.eps)
+
+
 def quick_gelu(x):
     return x * torch.sigmoid(1.702 * x)
 
