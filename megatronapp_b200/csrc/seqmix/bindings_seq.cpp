@@ -52,26 +52,33 @@ void add_rms_norm(Tensor x, c10::optional<Tensor> delta, const Tensor& w, Tensor
   count(); check_last_error("add_rms_norm");
 }
 
-void gated_head_rms_norm(const Tensor& o, const Tensor& w, c10::optional<Tensor> gate, Tensor y, double eps) {
+void gated_head_rms_norm(const Tensor& o, c10::optional<Tensor> w_opt, c10::optional<Tensor> gate, Tensor y, double eps, bool silu) {
   check_f32(o, "o");
   TORCH_CHECK(o.dim() == 3, "o must be [T, H, dv]");
   const bool bf16 = act_is_bf16(y, "y");
   const int T = static_cast<int>(o.size(0)), H = static_cast<int>(o.size(1)), dv = static_cast<int>(o.size(2));
   TORCH_CHECK(y.is_contiguous() && y.numel() == o.numel(), "y must be [T, H * dv]");
-  TORCH_CHECK(w.scalar_type() == y.scalar_type() && w.is_contiguous() && (w.numel() == dv || w.numel() == H * dv), "bad weight");
+  const void* wp = nullptr;
+  bool per_head = false;
+  if (w_opt.has_value() && w_opt->defined()) {
+    const Tensor& w = *w_opt;
+    TORCH_CHECK(w.is_cuda() && w.scalar_type() == y.scalar_type() && w.is_contiguous() && (w.numel() == dv || w.numel() == H * dv), "bad weight");
+    wp = w.data_ptr(); per_head = w.numel() != dv || H == 1;
+  }
   const void* gp = nullptr;
+  int64_t ldg = 0;
   if (gate.has_value() && gate->defined()) {
-    TORCH_CHECK(gate->scalar_type() == y.scalar_type() && gate->is_contiguous() && gate->numel() == o.numel(), "bad gate");
-    gp = gate->data_ptr();
+    TORCH_CHECK(gate->is_cuda() && gate->scalar_type() == y.scalar_type() && gate->dim() == 2 && gate->stride(1) == 1 && gate->size(0) == T &&
+                gate->size(1) == static_cast<int64_t>(H) * dv, "gate must be [T, H * dv] with unit inner stride");
+    gp = gate->data_ptr(); ldg = gate->stride(0);
   }
   c10::cuda::CUDAGuard g(o.device());
-  b200seq::gated_head_rms_norm(o.data_ptr<float>(), w.data_ptr(), gp, y.data_ptr(), T, H, dv, w.numel() != dv || H == 1, eps, bf16,
-                               cur_stream());
+  b200seq::gated_head_rms_norm(o.data_ptr<float>(), wp, gp, ldg, y.data_ptr(), T, H, dv, per_head, eps, silu, bf16, cur_stream());
   count(); check_last_error("gated_head_rms_norm");
 }
 
 void causal_conv(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, const Tensor& cu, const Tensor& rows,
-                 const Tensor& tok_seq, Tensor window, Tensor y, int64_t max_len, bool silu) {
+                 const Tensor& tok_seq, Tensor window, Tensor y, int64_t max_len, bool silu, bool residual) {
   const bool bf16 = act_is_bf16(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "x must be [T, C] with unit inner stride");
   const int T = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1)), taps = static_cast<int>(w.size(1));
@@ -88,7 +95,7 @@ void causal_conv(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias, c
   }
   c10::cuda::CUDAGuard g(x.device());
   b200seq::causal_conv_silu(x.data_ptr(), x.stride(0), w.data_ptr(), bp, cu.data_ptr<int>(), rows.data_ptr<int>(), tok_seq.data_ptr<int>(),
-                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), silu, bf16,
+                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), silu, residual, bf16,
                             cur_stream());
   count(2); check_last_error("causal_conv_silu");
 }
@@ -105,7 +112,8 @@ void delta_rule_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Te
   p.ldq = q.stride(0); p.ldk = k.stride(0); p.ldv = v.stride(0);
   p.H = static_cast<int>(v.size(1)); p.KH = static_cast<int>(q.size(1)); p.d = static_cast<int>(q.size(2)); p.dv = static_cast<int>(v.size(2));
   TORCH_CHECK(p.H % p.KH == 0 && k.size(1) == p.KH && k.size(2) == p.d, "bad head layout");
-  TORCH_CHECK(log_decay.numel() == q.size(0) * p.H * p.d && beta.numel() == q.size(0) * p.H, "bad decay / beta shape");
+  p.decay_per_head = log_decay.numel() == q.size(0) * p.H && (log_decay.dim() == 2 || p.d == 1) ? 1 : 0;
+  TORCH_CHECK((p.decay_per_head || log_decay.numel() == q.size(0) * p.H * p.d) && beta.numel() == q.size(0) * p.H, "bad decay / beta shape");
   TORCH_CHECK(state.dim() == 4 && state.size(1) == p.H && state.size(2) == p.d && state.size(3) == p.dv, "bad state shape");
   TORCH_CHECK(out.numel() == q.size(0) * p.H * p.dv, "bad out shape");
   p.log_decay = log_decay.data_ptr<float>(); p.beta = beta.data_ptr<float>();
@@ -198,25 +206,92 @@ void check_act2(const Tensor& t, const Tensor& like, const char* name) {   // [T
               " must be a [T, C] CUDA tensor with unit inner stride in the activation dtype");
 }
 
-void norm_add(Tensor x, const Tensor& a, c10::optional<Tensor> b, c10::optional<Tensor> wa, c10::optional<Tensor> wb, const Tensor& w,
-              Tensor y, double eps, double w_off) {
+void norm_add(Tensor x, const Tensor& a, c10::optional<Tensor> b, c10::optional<Tensor> wa, c10::optional<Tensor> wb,
+              c10::optional<Tensor> w, Tensor y, double eps, double w_off, c10::optional<Tensor> extra, c10::optional<Tensor> next_w) {
   check_f32(x, "x");
   const bool bf16 = act_is_bf16(y, "y");
   TORCH_CHECK(x.dim() == 2 && y.is_contiguous() && y.sizes() == x.sizes(), "x / y must be [rows, cols]");
-  TORCH_CHECK(a.scalar_type() == y.scalar_type() && a.is_contiguous() && a.sizes() == x.sizes(), "a must be contiguous, shaped like x");
-  TORCH_CHECK(w.scalar_type() == y.scalar_type() && w.is_contiguous() && w.numel() == x.size(1), "bad weight");
+  TORCH_CHECK(a.is_cuda() && a.scalar_type() == y.scalar_type() && a.is_contiguous() && a.sizes() == x.sizes(), "a must be contiguous, shaped like x");
   TORCH_CHECK(x.size(1) * sizeof(float) <= 48 * 1024, "row too wide");
+  auto vec = [&](const c10::optional<Tensor>& t, const char* name) -> const void* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == y.scalar_type() && t->is_contiguous() && t->numel() == x.size(1), name,
+                " must be a contiguous [cols] tensor in y's dtype");
+    return t->data_ptr();
+  };
   const bool two = b.has_value() && b->defined();
   if (two) {
-    TORCH_CHECK(b->scalar_type() == y.scalar_type() && b->is_contiguous() && b->sizes() == x.sizes(), "b must be shaped like a");
-    TORCH_CHECK(wa.has_value() && wb.has_value() && wa->scalar_type() == y.scalar_type() && wb->scalar_type() == y.scalar_type() &&
-                wa->is_contiguous() && wb->is_contiguous() && wa->numel() == x.size(1) && wb->numel() == x.size(1), "bad branch weights");
+    TORCH_CHECK(b->is_cuda() && b->scalar_type() == y.scalar_type() && b->is_contiguous() && b->sizes() == x.sizes(), "b must be shaped like a");
+    TORCH_CHECK(vec(wa, "weight_a") != nullptr && vec(wb, "weight_b") != nullptr, "two branches need their norm weights");
+  }
+  const void* ex = nullptr;
+  if (extra.has_value() && extra->defined()) {
+    TORCH_CHECK(extra->is_cuda() && extra->scalar_type() == y.scalar_type() && extra->is_contiguous() && extra->sizes() == x.sizes(),
+                "extra must be contiguous, shaped like x, in y's dtype");
+    ex = extra->data_ptr();
   }
   c10::cuda::CUDAGuard g(x.device());
-  b200seq::norm_add(x.data_ptr<float>(), a.data_ptr(), two ? b->data_ptr() : nullptr, two ? wa->data_ptr() : nullptr,
-                    two ? wb->data_ptr() : nullptr, w.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
-                    static_cast<float>(eps), static_cast<float>(w_off), bf16, cur_stream());
+  b200seq::norm_add(x.data_ptr<float>(), a.data_ptr(), two ? b->data_ptr() : nullptr, two ? vec(wa, "weight_a") : nullptr,
+                    two ? vec(wb, "weight_b") : nullptr, vec(w, "weight"), y.data_ptr(), static_cast<int>(x.size(0)),
+                    static_cast<int>(x.size(1)), static_cast<float>(eps), static_cast<float>(w_off), ex, vec(next_w, "next_weight"), bf16,
+                    cur_stream());
   count(); check_last_error("norm_add");
+}
+
+void retention_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& decay, c10::optional<Tensor> positions,
+                    c10::optional<Tensor> inv_freq, const Tensor& cu, const Tensor& rows, Tensor state, Tensor out, double k_scale,
+                    int64_t max_len) {
+  const bool bf16 = act_is_bf16(q, "q");
+  TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q / k / v dtypes differ");
+  check_rows(q, "q"); check_rows(k, "k"); check_rows(v, "v");
+  check_f32(decay, "decay"); check_f32(state, "state"); check_f32(out, "out");
+  check_i32(cu, "cu"); check_i32(rows, "rows");
+  b200seq::RetentionArgs p{};
+  p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr();
+  p.ldq = q.stride(0); p.ldk = k.stride(0); p.ldv = v.stride(0);
+  p.H = static_cast<int>(v.size(1)); p.d = static_cast<int>(q.size(2)); p.dv = static_cast<int>(v.size(2));
+  TORCH_CHECK(q.size(1) == p.H && k.size(1) == p.H && k.size(2) == p.d && v.size(0) == q.size(0) && k.size(0) == q.size(0), "bad head layout");
+  TORCH_CHECK(decay.numel() == p.H, "decay must be [H]");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == p.H && state.size(2) == p.d && state.size(3) == p.dv, "bad state shape");
+  TORCH_CHECK(out.numel() == q.size(0) * p.H * p.dv, "bad out shape");
+  if (inv_freq.has_value() && inv_freq->defined() && inv_freq->numel() > 0) {
+    check_f32(*inv_freq, "inv_freq");
+    p.n_rot = static_cast<int>(inv_freq->numel());
+    TORCH_CHECK(2 * p.n_rot <= p.d, "more rotated dimensions than the head has");
+    TORCH_CHECK(positions.has_value() && positions->is_cuda() && positions->scalar_type() == at::kLong && positions->is_contiguous() &&
+                positions->numel() == q.size(0), "positions must be a contiguous int64 [T]");
+    p.inv_freq = inv_freq->data_ptr<float>(); p.positions = positions->data_ptr<int64_t>();
+  }
+  p.decay = decay.data_ptr<float>();
+  p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>();
+  p.state = state.data_ptr<float>(); p.out = out.data_ptr<float>();
+  p.k_scale = static_cast<float>(k_scale);
+  p.max_len = max_len > 0 ? static_cast<int>(max_len) : (1 << 30);
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(b200seq::retention_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "retention_scan: key dim ", p.d,
+              " above the largest kernel instance (256)");
+  count(); check_last_error("retention_scan");
+}
+
+void poly_norm(const Tensor& z, const Tensor& coef, Tensor y, double eps) {
+  const bool bf16 = act_is_bf16(z, "z");
+  check_act2(z, z, "z"); check_f32(coef, "coef");
+  TORCH_CHECK(coef.numel() == 4, "coef must hold four numbers");
+  TORCH_CHECK(y.scalar_type() == z.scalar_type() && y.is_contiguous() && y.sizes() == z.sizes(), "bad y");
+  c10::cuda::CUDAGuard g(z.device());
+  TORCH_CHECK(b200seq::poly_norm(z.data_ptr(), z.stride(0), coef.data_ptr<float>(), y.data_ptr(), z.size(0), static_cast<int>(z.size(1)),
+                                 static_cast<float>(eps), bf16, cur_stream()), "poly_norm: row too wide");
+  count(); check_last_error("poly_norm");
+}
+
+void gelu_mul(const Tensor& gt, const Tensor& e, Tensor y) {
+  const bool bf16 = act_is_bf16(gt, "g");
+  check_act2(gt, gt, "g"); check_act2(e, gt, "e");
+  TORCH_CHECK(e.sizes() == gt.sizes() && y.scalar_type() == gt.scalar_type() && y.is_contiguous() && y.sizes() == gt.sizes(), "bad e / y");
+  c10::cuda::CUDAGuard g(gt.device());
+  b200seq::gelu_mul(gt.data_ptr(), gt.stride(0), e.data_ptr(), e.stride(0), y.data_ptr(), gt.size(0), static_cast<int>(gt.size(1)), bf16,
+                    cur_stream());
+  count(); check_last_error("gelu_mul");
 }
 
 void norm_rope(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor& wk, const Tensor& positions, const Tensor& inv_freq,
@@ -431,7 +506,7 @@ void head_rms_norm(const Tensor& x, const Tensor& w, Tensor y, double eps) {
 
 void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const Tensor& block_table, const Tensor& tok_req,
                             const Tensor& tok_len, c10::optional<Tensor> slopes, c10::optional<Tensor> gate, Tensor out, int64_t block_size,
-                            double scale, int64_t window, bool sink, double out_scale, int64_t max_len) {
+                            double scale, int64_t window, bool sink, double out_scale, int64_t max_len, c10::optional<Tensor> dist_bias) {
   const bool bf16 = act_is_bf16(q, "q");
   check_rows(q, "q");
   TORCH_CHECK(kcache.scalar_type() == q.scalar_type() && vcache.scalar_type() == q.scalar_type() && kcache.dim() == 3 && vcache.dim() == 3 &&
@@ -450,6 +525,11 @@ void window_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor&
     check_f32(*slopes, "slopes");
     TORCH_CHECK(slopes->numel() == p.H, "slopes must be [H]");
     p.slopes = slopes->data_ptr<float>();
+  }
+  if (dist_bias.has_value() && dist_bias->defined()) {
+    check_f32(*dist_bias, "dist_bias");
+    TORCH_CHECK(dist_bias->dim() == 2 && dist_bias->size(0) >= 1 && dist_bias->size(1) == p.H, "dist_bias must be [L, H]");
+    p.dist_bias = dist_bias->data_ptr<float>(); p.n_bias = static_cast<int>(dist_bias->size(0));
   }
   if (gate.has_value() && gate->defined()) {
     check_act2(*gate, q, "gate");
@@ -512,6 +592,9 @@ void selective_scan(const Tensor& x, c10::optional<Tensor> z, const Tensor& B, c
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rms_norm", &add_rms_norm);
+  m.def("retention_scan", &retention_scan);
+  m.def("poly_norm", &poly_norm);
+  m.def("gelu_mul", &gelu_mul);
   m.def("gated_head_rms_norm", &gated_head_rms_norm);
   m.def("causal_conv", &causal_conv);
   m.def("stream_mix_norm", &stream_mix_norm);

@@ -47,10 +47,10 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(float* __restrict__ x
   for (int c = threadIdx.x; c < cols; c += blockDim.x) st(y + base + c, row[c] * r * (w_off + ld(w + c)));
 }
 
-// one warp per (token, head): o / rms(o) * w * sigmoid(gate)
+// one warp per (token, head): o / rms(o) * w * act(gate), act = sigmoid or silu; w nullptr: no weight
 template <typename T>
-__global__ void gated_head_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ w, const T* __restrict__ gate,
-                                           T* __restrict__ y, int n_rows, int H, int dv, int w_per_head, float eps) {
+__global__ void gated_head_rms_norm_kernel(const float* __restrict__ o, const T* __restrict__ w, const T* __restrict__ gate, int64_t ldg,
+                                           T* __restrict__ y, int n_rows, int H, int dv, int w_per_head, float eps, int silu) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int lane = threadIdx.x & 31, h = row % H;
@@ -60,8 +60,12 @@ __global__ void gated_head_rms_norm_kernel(const float* __restrict__ o, const T*
   ss = warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / static_cast<float>(dv) + eps);
   for (int c = lane; c < dv; c += 32) {
-    float v = src[c] * r * ld(w + (w_per_head ? h * dv : 0) + c);
-    if (gate != nullptr) v *= sigmoidf_(ld(gate + static_cast<int64_t>(row) * dv + c));
+    float v = src[c] * r;
+    if (w != nullptr) v *= ld(w + (w_per_head ? h * dv : 0) + c);
+    if (gate != nullptr) {
+      const float gv = ld(gate + static_cast<int64_t>(row / H) * ldg + h * dv + c);
+      v *= silu ? gv * sigmoidf_(gv) : sigmoidf_(gv);
+    }
     st(y + static_cast<int64_t>(row) * dv + c, v);
   }
 }
@@ -85,7 +89,9 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, co
     const float in = src >= a ? ld(x + src * ldx + c) : ld(win + static_cast<int64_t>(taps - 1 + (src - a)) * C + c);
     acc += ld(w + static_cast<int64_t>(c) * taps + j) * in;
   }
-  st(y + static_cast<int64_t>(t) * C + c, silu ? acc * sigmoidf_(acc) : acc);
+  if (silu & 1) acc *= sigmoidf_(acc);
+  if (silu & 2) acc += ld(x + t * ldx + c);
+  st(y + static_cast<int64_t>(t) * C + c, acc);
 }
 
 // Two adjacent channels and a run of kConvRun tokens of one sequence per thread: every input is read once and slides through
@@ -129,7 +135,8 @@ __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __re
     float2 acc = bs;
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) { acc.x = fmaf(wt[j].x, hist[j].x, acc.x); acc.y = fmaf(wt[j].y, hist[j].y, acc.y); }
-    if (silu) acc = make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y));
+    if (silu & 1) acc = make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y));
+    if (silu & 2) { acc.x += hist[TAPS - 1].x; acc.y += hist[TAPS - 1].y; }
     Pair<T>::store(y + static_cast<int64_t>(t) * C + c, acc);
 #pragma unroll
     for (int j = 0; j < TAPS - 1; ++j) hist[j] = hist[j + 1];
@@ -201,7 +208,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
       const bool in = tt < nt && i < p.d;
       pq[s] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
       pk[s] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
-      pg[s] = in ? p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i] : 0.f;
+      pg[s] = in ? (p.decay_per_head ? p.log_decay[static_cast<int64_t>(t) * p.H + h] : p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 0.f;
     }
 #pragma unroll
     for (int s = 0; s < NV; ++s) {
@@ -232,7 +239,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
         const bool in = i < p.d;
         sq[tt][i] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
         sk[tt][i] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
-        sg[tt][i] = in ? expf(p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 1.f;
+        sg[tt][i] = in ? expf(p.decay_per_head ? p.log_decay[static_cast<int64_t>(t) * p.H + h] : p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 1.f;
       }
       for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {
         const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
@@ -677,13 +684,13 @@ void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows,
                            x, static_cast<const T*>(delta), static_cast<const T*>(w), static_cast<T*>(y), cols, eps, w_off));
 }
 
-void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
-                         float eps, bool bf16, cudaStream_t s) {
+void gated_head_rms_norm(const float* o, const void* w, const void* gate, int64_t ldg, void* y, int n_tok, int H, int dv,
+                         bool w_per_head, float eps, bool silu, bool bf16, cudaStream_t s) {
   const int rows = n_tok * H;
   if (rows == 0) return;
   SEQ_DISPATCH_T(bf16, gated_head_rms_norm_kernel<T><<<(rows + 3) / 4, 128, 0, s>>>(
-                           o, static_cast<const T*>(w), static_cast<const T*>(gate), static_cast<T*>(y), rows, H, dv,
-                           w_per_head ? 1 : 0, eps));
+                           o, static_cast<const T*>(w), static_cast<const T*>(gate), ldg, static_cast<T*>(y), rows, H, dv,
+                           w_per_head ? 1 : 0, eps, silu ? 1 : 0));
 }
 
 template <typename T, int TAPS>
@@ -698,9 +705,9 @@ static void launch_conv_run(const void* x, int64_t ldx, const void* w, const voi
 
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const void* bias, const int* cu, const int* rows, const int* tok_seq,
                       void* window,
-                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s) {
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool residual, bool bf16, cudaStream_t s) {
   if (n_tok == 0) return;
-  const int act = silu ? 1 : 0;
+  const int act = (silu ? 1 : 0) | (residual ? 2 : 0);
   const int64_t n = static_cast<int64_t>(n_tok) * C;
   // the paired kernel needs even channel counts and strides, 4- / 8-byte aligned bases, and a grid within the launch limits
   const size_t pair_bytes = bf16 ? 4 : 8;

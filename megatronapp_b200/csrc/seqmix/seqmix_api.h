@@ -9,7 +9,8 @@ namespace b200seq {
 struct DeltaArgs {
   const void *q, *k, *v;          // [T, KH, d], [T, KH, d], [T, H, dv] with row strides ldq / ldk / ldv (elements)
   int64_t ldq, ldk, ldv;
-  const float* log_decay;         // [T, H, d]
+  const float* log_decay;         // [T, H, d], or [T, H] with decay_per_head
+  int decay_per_head;
   const float* beta;              // [T, H]
   const int *cu, *rows;
   float* state;                   // [rows, H, d, dv]
@@ -43,10 +44,12 @@ struct LatentAttnArgs {
 };
 
 void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, float w_off, bool bf16, cudaStream_t s);
-void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
-                         float eps, bool bf16, cudaStream_t s);
+// w nullptr: no weight; gate [T, H * dv] with row stride ldg (nullptr: none), through a sigmoid or (silu) a SiLU
+void gated_head_rms_norm(const float* o, const void* w, const void* gate, int64_t ldg, void* y, int n_tok, int H, int dv,
+                         bool w_per_head, float eps, bool silu, bool bf16, cudaStream_t s);
+// residual: the input is added to the (activated) convolution
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const void* bias, const int* cu, const int* rows, const int* tok_seq, void* window,
-                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s);
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool residual, bool bf16, cudaStream_t s);
 bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s);
 bool mlstm_scan(const MlstmArgs& p, int R, bool bf16, cudaStream_t s);
 bool latent_attention_paged(const LatentAttnArgs& p, int n_tok, bool bf16, cudaStream_t s);
@@ -107,8 +110,10 @@ struct MinGruArgs {
   int C, max_runs;
 };
 
+// x += rms_norm(m) * (w_off + w) + extra, m = a or the mean of the two normed branches; w nullptr: m is added as it is;
+// y = the new x, or with next_w its RMS norm times next_w
 void norm_add(float* x, const void* a, const void* b, const void* wa, const void* wb, const void* w, void* y, int rows, int cols,
-              float eps, float w_off, bool bf16, cudaStream_t s);
+              float eps, float w_off, const void* extra, const void* next_w, bool bf16, cudaStream_t s);
 void norm_rope(const NormRopeArgs& p, int n_tok, bool bf16, cudaStream_t s);
 int mixed_attention_splits(int n_tok, int max_len);
 bool mixed_attention_paged(const MixAttnArgs& p, int n_tok, bool bf16, cudaStream_t s);
@@ -139,6 +144,8 @@ struct WindowAttnArgs {
   const void *kcache, *vcache;    // [slots, G, d], [slots, G, dv]
   const int *block_table, *tok_req, *tok_len;
   const float* slopes;            // [H] distance penalty per head (nullptr: none)
+  const float* dist_bias;         // [n_bias, H] added to the score by distance, the last row for larger distances (nullptr: none)
+  int n_bias;
   const void* gate;               // [T, H] pre-activation of the per-head output gate, row stride ldg (nullptr: none)
   int64_t ldg;
   void* out;                      // [T, H * dv]
@@ -172,5 +179,24 @@ bool window_attention_paged(const WindowAttnArgs& p, bool bf16, cudaStream_t s);
 // key splits for a batch of n_tok single-token sequences whose longest visible context is max_keys
 int window_attention_splits(int H, int G, int n_tok, int max_keys);
 bool selective_scan(const SelScanArgs& p, int R, bool bf16, cudaStream_t s);
+
+struct RetentionArgs {
+  const void *q, *k, *v;          // [T, H, d], [T, H, d], [T, H, dv] with row strides ldq / ldk / ldv (elements)
+  int64_t ldq, ldk, ldv;
+  const float* decay;             // [H]
+  const int64_t* positions;       // [T] (nullptr with n_rot = 0)
+  const float* inv_freq;          // [n_rot]: dimension i of a head turns with dimension i + n_rot
+  const int *cu, *rows;
+  float* state;                   // [rows, H, d, dv]
+  float* out;                     // [T, H, dv]
+  int H, d, dv, n_rot;
+  int max_len;                    // the longest sequence of the step (0: unknown)
+  float k_scale;
+};
+bool retention_scan(const RetentionArgs& p, int R, bool bf16, cudaStream_t s);
+// y = a N(z) + b N(z^2) + c N(z^3) + e per row, N = division by the root mean square; coef = (a, b, c, e) fp32 on the device
+bool poly_norm(const void* z, int64_t ldz, const float* coef, void* y, int64_t rows, int cols, float eps, bool bf16, cudaStream_t s);
+// y = gelu_tanh(g) * e
+void gelu_mul(const void* g, int64_t ldg, const void* e, int64_t lde, void* y, int64_t rows, int cols, bool bf16, cudaStream_t s);
 
 }  // namespace b200seq

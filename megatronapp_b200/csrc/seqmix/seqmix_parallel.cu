@@ -40,7 +40,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {   // every thr
 template <typename T>
 __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ x, const T* __restrict__ a, const T* __restrict__ b,
                                                        const T* __restrict__ wa, const T* __restrict__ wb, const T* __restrict__ w,
-                                                       T* __restrict__ y, int cols, float eps, float w_off) {
+                                                       T* __restrict__ y, int cols, float eps, float w_off,
+                                                       const T* __restrict__ extra, const T* __restrict__ next_w) {
   extern __shared__ float row[];
   __shared__ float red[32];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * cols;
@@ -58,13 +59,24 @@ __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ x, co
   } else {
     for (int c = threadIdx.x; c < cols; c += blockDim.x) row[c] = ld(a + base + c);
   }
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) ss += row[c] * row[c];   // each thread re-reads its own entries
-  const float r = 1.0f / sqrtf(block_sum(ss, red) * inv_n + eps);
+  float r = 1.f;
+  if (w != nullptr) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) ss += row[c] * row[c];   // each thread re-reads its own entries
+    r = 1.0f / sqrtf(block_sum(ss, red) * inv_n + eps);
+  }
+  float sx = 0.f;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    const float v = x[base + c] + row[c] * r * (w_off + ld(w + c));
+    float m = w != nullptr ? row[c] * r * (w_off + ld(w + c)) : row[c];
+    if (extra != nullptr) m += ld(extra + base + c);
+    const float v = x[base + c] + m;
     x[base + c] = v;
-    st(y + base + c, v);
+    if (next_w != nullptr) { row[c] = v; sx += v * v; }
+    else st(y + base + c, v);
+  }
+  if (next_w != nullptr) {
+    const float rx = 1.0f / sqrtf(block_sum(sx, red) * inv_n + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) st(y + base + c, row[c] * rx * ld(next_w + c));
   }
 }
 
@@ -888,11 +900,12 @@ __global__ void clamped_glu_vec_kernel(const T* __restrict__ x, int64_t ldx, T* 
 // launchers
 // ---------------------------------------------------------------------------------------------------------------------
 void norm_add(float* x, const void* a, const void* b, const void* wa, const void* wb, const void* w, void* y, int rows, int cols,
-              float eps, float w_off, bool bf16, cudaStream_t s) {
+              float eps, float w_off, const void* extra, const void* next_w, bool bf16, cudaStream_t s) {
   if (rows == 0) return;
   SEQ_DISPATCH_T(bf16, norm_add_kernel<T><<<rows, 256, cols * sizeof(float), s>>>(
                            x, static_cast<const T*>(a), static_cast<const T*>(b), static_cast<const T*>(wa),
-                           static_cast<const T*>(wb), static_cast<const T*>(w), static_cast<T*>(y), cols, eps, w_off));
+                           static_cast<const T*>(wb), static_cast<const T*>(w), static_cast<T*>(y), cols, eps, w_off,
+                           static_cast<const T*>(extra), static_cast<const T*>(next_w)));
 }
 
 void norm_rope(const NormRopeArgs& p, int n_tok, bool bf16, cudaStream_t s) {

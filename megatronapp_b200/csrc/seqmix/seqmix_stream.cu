@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(128) head_rms_norm_kernel(const T* __restrict_
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Paged grouped-query attention with a sliding window.  Query at position i sees keys j with 0 <= i - j < window (window 0:
-// all keys up to i); score = q . k * scale - slope[h] * (i - j); weights exp(s_j) / (sink + sum_j exp(s_j)) where the sink
+// all keys up to i); score = q . k * scale - slope[h] * (i - j) + dist_bias[min(i - j, n_bias - 1)][h]; weights exp(s_j) / (sink + sum_j exp(s_j)) where the sink
 // (0 or 1) is a key of score 0 without a value; the head's output is multiplied by sigmoid(gate[t, h]) and out_scale.
 //
 // grid (query blocks, kv heads, head chunks x key splits).  A CTA takes QB consecutive packed tokens and HC heads of one kv
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
           ld(qbase + static_cast<int64_t>(seg + qi) * p.ldq + static_cast<int64_t>(g * rep + h_lo + hh) * d + c) * p.scale;
     }
     float m[kWinSlots], l[kWinSlots], acc[kWinSlots][DVR], slope[kWinSlots];
-    int pos[kWinSlots], lo[kWinSlots];
+    int pos[kWinSlots], lo[kWinSlots], hd[kWinSlots];
     const bool with_sink = p.sink != 0;
 #pragma unroll
     for (int u = 0; u < kWinSlots; ++u) {
@@ -330,9 +330,10 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
       l[u] = with_sink ? 1.f : 0.f;
 #pragma unroll
       for (int k = 0; k < DVR; ++k) acc[u][k] = 0.f;
-      pos[u] = -1; lo[u] = 0; slope[u] = 0.f;
+      pos[u] = -1; lo[u] = 0; slope[u] = 0.f; hd[u] = 0;
       if (u < ns) {
         const int pr = warp + u * NW, qi = pr / n_heads, hh = pr % n_heads;
+        hd[u] = g * rep + h_lo + hh;
         pos[u] = p.tok_len[seg + qi] - 1;
         lo[u] = p.window > 0 ? max(0, pos[u] + 1 - p.window) : 0;
         slope[u] = p.slopes != nullptr ? p.slopes[g * rep + h_lo + hh] : 0.f;
@@ -376,7 +377,8 @@ __global__ void __launch_bounds__(kWinWarps * 32) window_attention_kernel(Window
         pw[u] = 0.f;
         if (u < ns) {
           const bool vis = lane < n_keys && key <= pos[u] && key >= lo[u];
-          const float sc = vis ? s[u] - slope[u] * static_cast<float>(pos[u] - key) : -INFINITY;
+          float sc = vis ? s[u] - slope[u] * static_cast<float>(pos[u] - key) : -INFINITY;
+          if (vis && p.dist_bias != nullptr) sc += p.dist_bias[static_cast<int64_t>(min(pos[u] - key, p.n_bias - 1)) * p.H + hd[u]];
           const float m_new = fmaxf(m[u], warp_max(sc));
           float corr = 1.f;
           if (m_new != -INFINITY) {
@@ -592,6 +594,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) window_attention_decode_ker
     }
     float pw[NP];
     const float dist = static_cast<float>(pos - key);
+    const float* brow = (p.dist_bias != nullptr && vis) ? p.dist_bias + static_cast<int64_t>(min(pos - key, p.n_bias - 1)) * p.H + g * rep + h_lo
+                                                        : nullptr;
 #pragma unroll
     for (int u = 0; u < NP; ++u) {
       pw[u] = 0.f;
@@ -599,7 +603,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 4) window_attention_decode_ker
         float su = s[u];
         su += __shfl_xor_sync(0xffffffffu, su, 1);
         su += __shfl_xor_sync(0xffffffffu, su, 2);
-        const float sc = vis ? su - slope[u] * dist : -INFINITY;
+        float sc = vis ? su - slope[u] * dist : -INFINITY;
+        if (brow != nullptr) sc += brow[u];
         const float m_new = fmaxf(m[u], warp_max(sc));     // finite: the warp's first key is visible
         pw[u] = vis ? expf(sc - m_new) : 0.f;
         const float corr = expf(m[u] - m_new);             // m = -inf: 0, and l and acc are 0 then
