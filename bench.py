@@ -441,7 +441,7 @@ def main():
                     help="instead of the training step: prefill / decode throughput of the hybrid (Zikunex) design beside the closest "
                          "existing model through the dynamic engine, and its kernels against their rooflines (1 GPU)")
     ap.add_argument("--serving-size", default="medium", choices=["small", "medium"])
-    ap.add_argument("--serving-design", default="zikunex", choices=["zikunex", "lerorax", "domasun"],
+    ap.add_argument("--serving-design", default="zikunex", choices=["zikunex", "lerorax", "domasun", "nunosun"],
                     help="--serving: which hybrid design to measure beside its closest existing model")
     ap.add_argument("--serving-models-only", action="store_true", help="--serving: skip the per-kernel numbers")
     args = ap.parse_args()

@@ -3,7 +3,8 @@ attention and the same feed-forwards, both through ``DynamicInferenceEngine.forw
 with ``--serving-design lerorax`` the Lerorax design beside its closest existing model, Zikunex, at equal width, depth and
 head sizes, and the Lerorax kernels beside their like kernels; with ``--serving-design domasun`` the Domasun design beside its
 closest existing model, Lerorax (two mixers side by side on a paged attention and a recurrent memory), and its kernels
-beside their like kernels.
+beside their like kernels; with ``--serving-design nunosun`` the Nunosun design beside its closest existing model, Domasun
+(sliding-window attention beside a recurrent memory, mixtures of experts), and its kernels beside their like kernels.
 
 Two parts, random weights, bf16:
 
@@ -157,6 +158,35 @@ def build_domasun(s, device):
     dcfg = DomasunConfig.from_dict(domasun_config(s))
     base = dcfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
     return DomasunModel(dcfg, base).to(device).eval()
+
+
+def nunosun_config(s):
+    """A Nunosun stack at the sizes of ``s``: gated delta-rule layers with a dense PolyNorm feed-forward in turn with layers of
+    sliding-window attention (a window of 1024, 32 distance buckets) beside a retention memory and a mixture of SiLU-gated
+    experts; a three-tap convolution in front of every mixer and a per-layer token vector of 64 numbers."""
+    H, d = s["heads"], s["dim"]
+    left = {"heads": H, "kv_heads": max(1, H // 4), "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": 1024}, "bias_max": 1024,
+            "bias_buckets": 32}
+    right = {"heads": H, "dim": 64, "vdim": d, "decay": [1.0 - 2.0 ** (-5 - 3.0 * h / max(1, H - 1)) for h in range(H)],
+             "rot": {"dims": 64, "base": 10000.0}}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    delta = {"heads": H, "kv_heads": max(1, H // 2), "dim": 64, "vdim": d, "conv": 4}
+    layers = [{"type": "delta", "mixer": delta, "mlp": dense} if i % 2 == 0 else
+              {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": moe} for i in range(s["layers"])]
+    return {"architecture": "Nunosun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "canon": {"taps": 3},
+            "token_side": {"dim": 64}, "logit_scale": 0.5, "layers": layers}
+
+
+def build_nunosun(s, device):
+    from .models.nunosun import NunosunConfig, NunosunModel
+    from .parallel import state as ps
+
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_model_parallel(1, 1)
+    ncfg = NunosunConfig.from_dict(nunosun_config(s))
+    base = ncfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
+    return NunosunModel(ncfg, base).to(device).eval()
 
 
 def _engine(model, max_tokens, max_requests):
@@ -413,6 +443,103 @@ def kernel_numbers_domasun(s, device):
     return out, roof
 
 
+def kernel_numbers_nunosun(s, device):
+    """The kernels of the Nunosun layers alone, each beside the like kernel of the closest models (Domasun, Zikunex)."""
+    from .ops import seqmix
+    from .transformer.window_attention import distance_buckets, distance_slopes
+
+    bench, out, roof = _kernel_bench(device)
+    H, d, W = s["heads"], s["dim"], s["width"]
+    G = max(1, H // 4)
+    bf = torch.bfloat16
+    rn = lambda *sh, **kw: torch.randn(*sh, device=device, **kw)  # noqa: E731
+    # -- decode attention: 64 requests x 2048 cached tokens of which a window of 1024 is visible; prefill: one prompt of 2048
+    R, L, bs, win = 64, 2048, 16, 1024
+    nblk = R * L // bs
+    table = torch.randperm(nblk, device=device).to(torch.int32).view(R, L // bs)
+    req = torch.arange(R, dtype=torch.int32, device=device)
+    lens = torch.full((R,), L, dtype=torch.int32, device=device)
+    kc, vc = rn(nblk * bs, G, d, dtype=bf), rn(nblk * bs, G, d, dtype=bf)
+    slopes = distance_slopes(H).to(device)
+    bias = rn(32, H)[distance_buckets(32, 1024.0, win).to(device)].contiguous()
+    q, gate = rn(R, H, d, dtype=bf), rn(R, H, dtype=bf)
+    bench("window_attention_paged.decode (distance bias)",
+          lambda: seqmix.window_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, win, None, False, None, 1.0, L, bias),
+          R * win * G * d * 2 * 2, flops=R * win * H * d * 4, like="window_attention_paged.decode (slopes, sink, gate)")
+    bench("window_attention_paged.decode (slopes, sink, gate)",
+          lambda: seqmix.window_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, win, slopes, True, gate, 1.0, L),
+          R * win * G * d * 2 * 2, flops=R * win * H * d * 4)
+    T = 2048
+    table1 = torch.randperm(T // bs, device=device).to(torch.int32).view(1, -1)
+    req1 = torch.zeros(T, dtype=torch.int32, device=device)
+    len1 = torch.arange(1, T + 1, dtype=torch.int32, device=device)
+    q1, gate1 = rn(T, H, d, dtype=bf), rn(T, H, dtype=bf)
+    pairs = win * (win + 1) / 2 + (T - win) * win                     # visible (query, key) pairs under the window
+    bench("window_attention_paged.prefill (distance bias)",
+          lambda: seqmix.window_attention_paged(q1, kc, vc, table1, req1, len1, bs, d ** -0.5, win, None, False, None, 1.0, 0, bias),
+          T * G * d * 4 + T * H * d * 4, flops=pairs * H * d * 4, like="window_attention_paged.prefill (slopes, sink, gate)")
+    bench("window_attention_paged.prefill (slopes, sink, gate)",
+          lambda: seqmix.window_attention_paged(q1, kc, vc, table1, req1, len1, bs, d ** -0.5, win, slopes, True, gate1),
+          T * G * d * 4 + T * H * d * 4, flops=pairs * H * d * 4)
+    # -- matrix memories: decode (64 sequences x 1 token, state bound) and prefill (4 x 2048 tokens, FMA bound); key dim 64
+    dd = 64
+    for tag, R_, n in (("decode", 64, 1), ("prefill", 4, 2048)):
+        T_ = R_ * n
+        pb = seqmix.PackedBatch([i * n for i in range(R_ + 1)], list(range(R_)), device)
+        qq, k, v = rn(T_, H, dd, dtype=bf), rn(T_, H, dd, dtype=bf), rn(T_, H, d, dtype=bf)
+        S = torch.zeros(R_, H, dd, d, device=device)
+        state_bytes = R_ * H * dd * d * 4 * 2
+        decay = torch.rand(H, device=device) * 0.05 + 0.95
+        pos = torch.arange(n, device=device).repeat(R_) + (1024 if n == 1 else 0)
+        inv = seqmix.rotary_frequencies(dd, 10000.0, device)
+        bench(f"retention_scan.{tag}", lambda: seqmix.retention_scan(qq, k, v, decay, pb, S, pos, inv, dd ** -0.5),
+              state_bytes + T_ * H * (2 * dd + d) * 2 + T_ * H * d * 4, flops=T_ * H * dd * d * 4, like=f"delta_rule_scan.{tag} (decay per channel)")
+        ldc = -torch.rand(T_, H, dd, device=device) * 0.1
+        ldh = -torch.rand(T_, H, device=device) * 0.1
+        beta = torch.rand(T_, H, device=device)
+        kq, kk = rn(T_, H // 2, dd, dtype=bf), rn(T_, H // 2, dd, dtype=bf)
+        io = T_ * (H // 2) * dd * 2 * 2 + T_ * H * d * 2 + T_ * H * d * 4
+        bench(f"delta_rule_scan.{tag} (decay per head)", lambda: seqmix.delta_rule_scan(kq, kk, v, ldh, beta, pb, S, 1e-6, dd ** -0.5),
+              state_bytes + io + T_ * H * 8, flops=T_ * H * dd * d * 8, like=f"delta_rule_scan.{tag} (decay per channel)")
+        bench(f"delta_rule_scan.{tag} (decay per channel)", lambda: seqmix.delta_rule_scan(kq, kk, v, ldc, beta, pb, S, 1e-6, dd ** -0.5),
+              state_bytes + io + T_ * H * (dd + 1) * 4, flops=T_ * H * dd * d * 8)
+    # -- additions and norms, convolution, activations over 8192 tokens
+    T = 8192
+    x = rn(T, W)
+    a, b, f = rn(T, W, dtype=bf), rn(T, W, dtype=bf), rn(T, W, dtype=bf)
+    w = torch.ones(W, device=device, dtype=bf)
+    bench("norm_add (two branches + feed-forward, no outer norm)", lambda: seqmix.norm_add(x, a, None, 1e-6, bf, 0.0, b, w, w, extra=f),
+          T * W * (4 + 4 + 2 + 2 + 2 + 2), like="norm_add (two branches)")
+    bench("norm_add (normed addend + next norm)", lambda: seqmix.norm_add(x, a, w, 1e-6, bf, next_weight=w), T * W * (4 + 4 + 2 + 2),
+          like="norm_add (two branches)")
+    bench("norm_add (two branches)", lambda: seqmix.norm_add(x, a, w, 1e-5, bf, 1.0, b, w, w), T * W * (4 + 4 + 2 + 2 + 2))
+    bench("add_rms_norm", lambda: seqmix.add_rms_norm(x, a, w, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+    o = rn(T, H, d)
+    gt = rn(T, H * d, dtype=bf)
+    wn = torch.ones(d, device=device, dtype=bf)
+    bench("gated_head_rms_norm (no weight, silu gate)", lambda: seqmix.gated_head_rms_norm(o, None, gt, 1e-6, bf, "silu"), T * H * d * (4 + 2 + 2),
+          like="gated_head_rms_norm (weight, sigmoid gate)")
+    bench("gated_head_rms_norm (weight, sigmoid gate)", lambda: seqmix.gated_head_rms_norm(o, wn, gt, 1e-6, bf), T * H * d * (4 + 2 + 2))
+    h = rn(T, W, dtype=bf)
+    wc3 = rn(W, 3, dtype=bf)
+    pbc = seqmix.PackedBatch([0, T], [0], device)
+    win3 = torch.zeros(1, 2, W, device=device, dtype=bf)
+    bench("causal_conv (3 taps, input added)", lambda: seqmix.causal_conv(h, wc3, pbc, win3, residual=True), T * W * 4, like="causal_conv_silu")
+    C = (H + H // 2 * 2) * 64
+    xc, wc = rn(T, C, dtype=bf), rn(C, 4, dtype=bf)
+    winc = torch.zeros(1, 3, C, device=device, dtype=bf)
+    bench("causal_conv_silu", lambda: seqmix.causal_conv_silu(xc, wc, pbc, winc), T * C * 4)
+    F_ = s["ff"]
+    z = rn(T, F_, dtype=bf)
+    coef = torch.tensor([0.8, 0.3, -0.2, 0.1], device=device)
+    bench("poly_norm", lambda: seqmix.poly_norm(z, coef, 1e-6), T * F_ * 4, like="clamped_glu")
+    z2 = rn(T, 2 * F_, dtype=bf)
+    bench("clamped_glu", lambda: seqmix.clamped_glu(z2, 7.0), T * F_ * 6)
+    g64, e64 = rn(T, 64, dtype=bf), rn(T, 64 * s["layers"], dtype=bf)
+    bench("gelu_mul", lambda: seqmix.gelu_mul(g64, e64[:, 64:128]), T * 64 * 6, like="clamped_glu")
+    return out, roof
+
+
 def kernel_numbers(s, device):
     """Every new kernel alone and its like kernel: time, achieved bytes/s (or flop/s) and the fraction of the roofline."""
     from . import ops
@@ -539,7 +666,8 @@ def run(args):
     res["design"] = design
     pairs = {"zikunex": (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)),
              "lerorax": (("lerorax", build_lerorax), ("zikunex", build_zikunex)),
-             "domasun": (("domasun", build_domasun), ("lerorax", build_lerorax))}[design]
+             "domasun": (("domasun", build_domasun), ("lerorax", build_lerorax)),
+             "nunosun": (("nunosun", build_nunosun), ("domasun", build_domasun))}[design]
     with torch.no_grad():
         for name, build in pairs:
             t0 = time.time()
@@ -551,7 +679,8 @@ def run(args):
             del model
             torch.cuda.empty_cache()
         if not getattr(args, "serving_models_only", False):
-            fn = {"zikunex": kernel_numbers, "lerorax": kernel_numbers_lerorax, "domasun": kernel_numbers_domasun}[design]
+            fn = {"zikunex": kernel_numbers, "lerorax": kernel_numbers_lerorax, "domasun": kernel_numbers_domasun,
+                  "nunosun": kernel_numbers_nunosun}[design]
             res["kernels"], res["roofline"] = fn(s, dev)
     print(json.dumps(res), flush=True)
     return res
