@@ -640,3 +640,17 @@ def test_model_folder_through_registry_and_trace_runner_command_line(tmp_path):
     got2 = torch.frombuffer(bytearray((out / "2.f32").read_bytes()), dtype=torch.float32).view(1, -1)
     close(got0, want[[0, 8]], TOL[torch.float32])
     close(got2, want[[11]], TOL[torch.float32])
+    # the generation command line on the same folder: greedy tokens of the oracle (a close call is no test)
+    prompt, gen = toks[:7], []
+    for _ in range(4):
+        top2 = torch.topk(oracle.forward(cfg, W, prompt + gen)[-1], 2)
+        if float(top2.values[0] - top2.values[1]) < 1e-3:
+            break
+        gen.append(int(top2.indices[0]))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "tools", "run_text_generation_server.py"), "--model-dir", str(folder),
+                        "--dtype", "float32", "--prompts", " ".join(map(str, prompt)), "--num-tokens-to-generate", "4"],
+                       capture_output=True, text=True, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""), timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    said = r.stdout.strip().splitlines()[-1].split("-> ")[-1].strip("'\"").split()
+    assert [int(t) for t in said][:len(gen)] == gen
