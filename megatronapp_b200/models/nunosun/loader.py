@@ -25,7 +25,7 @@ import torch
 
 from ..zikunex.loader import _copy, read_safetensors
 
-DEFAULT_BIAS_BUCKETS = 32           # for a folder without weights whose config does not say
+DEFAULT_BIAS_BUCKETS = 16           # for a folder without weights whose config does not say
 
 
 def shapes_into_config(config: dict, shapes: Dict[str, tuple]) -> dict:
