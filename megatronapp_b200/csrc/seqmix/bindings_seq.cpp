@@ -284,6 +284,22 @@ void poly_norm(const Tensor& z, const Tensor& coef, Tensor y, double eps) {
   count(); check_last_error("poly_norm");
 }
 
+void decay_gates(const Tensor& a, const Tensor& b, const Tensor& A_log, const Tensor& dt_bias, Tensor log_decay, Tensor beta) {
+  const bool bf16 = act_is_bf16(a, "a");
+  check_act2(a, a, "a"); check_act2(b, a, "b");
+  check_f32(log_decay, "log_decay"); check_f32(beta, "beta");
+  const int64_t rows = a.size(0);
+  const int C = static_cast<int>(a.size(1)), H = static_cast<int>(b.size(1));
+  TORCH_CHECK(b.size(0) == rows && H > 0 && C % H == 0, "a must be [T, C] and b [T, H] with C a multiple of H");
+  TORCH_CHECK(A_log.is_cuda() && A_log.scalar_type() == a.scalar_type() && A_log.is_contiguous() && A_log.numel() == H &&
+              dt_bias.is_cuda() && dt_bias.scalar_type() == a.scalar_type() && dt_bias.is_contiguous() && dt_bias.numel() == C, "bad A_log / dt_bias");
+  TORCH_CHECK(log_decay.numel() == rows * C && beta.numel() == rows * H, "bad output shapes");
+  c10::cuda::CUDAGuard g(a.device());
+  b200seq::decay_gates(a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), A_log.data_ptr(), dt_bias.data_ptr(), log_decay.data_ptr<float>(),
+                       beta.data_ptr<float>(), rows, C, H, bf16, cur_stream());
+  count(); check_last_error("decay_gates");
+}
+
 void gelu_mul(const Tensor& gt, const Tensor& e, Tensor y) {
   const bool bf16 = act_is_bf16(gt, "g");
   check_act2(gt, gt, "g"); check_act2(e, gt, "e");
@@ -595,6 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("retention_scan", &retention_scan);
   m.def("poly_norm", &poly_norm);
   m.def("gelu_mul", &gelu_mul);
+  m.def("decay_gates", &decay_gates);
   m.def("gated_head_rms_norm", &gated_head_rms_norm);
   m.def("causal_conv", &causal_conv);
   m.def("stream_mix_norm", &stream_mix_norm);

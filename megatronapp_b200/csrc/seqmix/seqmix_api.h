@@ -196,6 +196,9 @@ struct RetentionArgs {
 bool retention_scan(const RetentionArgs& p, int R, bool bf16, cudaStream_t s);
 // y = a N(z) + b N(z^2) + c N(z^3) + e per row, N = division by the root mean square; coef = (a, b, c, e) fp32 on the device
 bool poly_norm(const void* z, int64_t ldz, const float* coef, void* y, int64_t rows, int cols, float eps, bool bf16, cudaStream_t s);
+// log_decay [rows, C] = -exp(A_log[c / (C / H)]) * softplus(a + dt_bias), beta [rows, H] = sigmoid(b); a [rows, C], b [rows, H] with row strides
+void decay_gates(const void* a, int64_t lda, const void* b, int64_t ldb, const void* A_log, const void* dt_bias, float* log_decay, float* beta,
+                 int64_t rows, int C, int H, bool bf16, cudaStream_t s);
 // y = gelu_tanh(g) * e
 void gelu_mul(const void* g, int64_t ldg, const void* e, int64_t lde, void* y, int64_t rows, int cols, bool bf16, cudaStream_t s);
 

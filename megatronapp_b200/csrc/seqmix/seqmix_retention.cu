@@ -235,6 +235,26 @@ __global__ void gelu_mul_kernel(const T* __restrict__ g, int64_t ldg, const T* _
   st(y + idx, act * ld(e + r * lde + c));
 }
 
+// log_decay = -exp(A_log[head]) * softplus(a + dt_bias), beta = sigmoid(b): the gates of the delta rule from the projections'
+// pre-activations, fp32 out.  C decay channels per row, C / H per head.
+template <typename T>
+__global__ void decay_gates_kernel(const T* __restrict__ a, int64_t lda, const T* __restrict__ b, int64_t ldb, const T* __restrict__ A_log,
+                                   const T* __restrict__ dt_bias, float* __restrict__ log_decay, float* __restrict__ beta, int64_t rows,
+                                   int C, int H) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int per = C + H;                              // a row's decay channels, then its betas
+  if (idx >= rows * per) return;
+  const int64_t r = idx / per;
+  const int c = static_cast<int>(idx - r * per);
+  if (c < C) {
+    const float z = ld(a + r * lda + c) + ld(dt_bias + c);
+    const float sp = z > 20.f ? z : log1pf(expf(z));
+    log_decay[r * C + c] = -expf(ld(A_log + c / (C / H))) * sp;
+  } else {
+    beta[r * H + (c - C)] = sigmoidf_(ld(b + r * ldb + (c - C)));
+  }
+}
+
 template <typename T>
 static bool launch_retention(const RetentionArgs& p, dim3 grid, cudaStream_t s) {
 #define SEQ_RET(DD)                                                                                       \
@@ -273,6 +293,15 @@ bool poly_norm(const void* z, int64_t ldz, const float* coef, void* y, int64_t r
     else poly_norm_kernel<float, 1><<<grid, 256, 0, s>>>(static_cast<const float*>(z), ldz, coef, static_cast<float*>(y), cols, eps);
   }
   return true;
+}
+
+void decay_gates(const void* a, int64_t lda, const void* b, int64_t ldb, const void* A_log, const void* dt_bias, float* log_decay, float* beta,
+                 int64_t rows, int C, int H, bool bf16, cudaStream_t s) {
+  const int64_t n = rows * (C + H);
+  if (n == 0) return;
+  SEQ_DISPATCH_T(bf16, decay_gates_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
+                           static_cast<const T*>(a), lda, static_cast<const T*>(b), ldb, static_cast<const T*>(A_log),
+                           static_cast<const T*>(dt_bias), log_decay, beta, rows, C, H));
 }
 
 void gelu_mul(const void* g, int64_t ldg, const void* e, int64_t lde, void* y, int64_t rows, int cols, bool bf16, cudaStream_t s) {

@@ -222,6 +222,27 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay
     return o
 
 
+def decay_gates(a_pre: torch.Tensor, b_pre: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The delta rule's gates from the projections' pre-activations ``a_pre [T, C]`` and ``b_pre [T, H]`` (column slices of a
+    fused projection are fine), ``A_log [H]``, ``dt_bias [C]`` with ``C = H`` (one decay per head) or ``C = H * d`` (one per key
+    channel)::
+
+        log_decay = -exp(A_log[head]) * softplus(a_pre + dt_bias);   beta = sigmoid(b_pre)
+
+    Both fp32, ``[T, C]`` and ``[T, H]``."""
+    T, C = a_pre.shape
+    H = b_pre.shape[1]
+    if a_pre.is_cuda:
+        kernel_calls["decay_gates"] += 1
+        log_decay = torch.empty(T, C, dtype=torch.float32, device=a_pre.device)
+        beta = torch.empty(T, H, dtype=torch.float32, device=a_pre.device)
+        ext().decay_gates(a_pre if a_pre.stride(1) == 1 else a_pre.contiguous(), b_pre if b_pre.stride(1) == 1 else b_pre.contiguous(),
+                          A_log.contiguous(), dt_bias.contiguous(), log_decay, beta)
+        return log_decay, beta
+    rate = torch.exp(A_log.float()).repeat_interleave(C // H)
+    return -rate * F.softplus(a_pre.float() + dt_bias.float()), torch.sigmoid(b_pre.float())
+
+
 # ---------------------------------------------------------------------------
 # mLSTM matrix memory with stabilised exponential gates
 # ---------------------------------------------------------------------------

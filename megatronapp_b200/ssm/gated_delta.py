@@ -99,12 +99,9 @@ class GatedDeltaMixer(MegatronModule):
         T = qkv.shape[0]
         q, k, v = torch.split(qkv, [self.qk_ch, self.qk_ch, self.v_ch], dim=-1)
         dt = self.decay_up(a1.contiguous())[0] if self.decay_up is not None else a1
-        if self.decay_per_head:
-            log_decay = -torch.exp(self.A_log.float()) * F.softplus(dt.float() + self.dt_bias.float())          # [T, H]
-        else:
-            log_decay = -torch.exp(self.A_log.float()).view(1, self.nh, 1) * F.softplus(
-                dt.float() + self.dt_bias.float()).view(T, self.nh, self.d)
-        beta = torch.sigmoid(braw.float())
+        log_decay, beta = seqmix.decay_gates(dt, braw, self.A_log, self.dt_bias)         # fp32 [T, H] or [T, H * d], [T, H]
+        if not self.decay_per_head:
+            log_decay = log_decay.view(T, self.nh, self.d)
         o = seqmix.delta_rule_scan(q.reshape(T, self.nkv, self.d), k.reshape(T, self.nkv, self.d),
                                    v.reshape(T, self.nh, self.dv), log_decay, beta, pb, state, self.unit_eps,
                                    self.d ** -0.5)

@@ -210,6 +210,13 @@ def test_ops_match_the_oracle_functions(device):
     want = oracle.delta_rule((oracle.unit(qd.double()) * dd ** -0.5).repeat_interleave(2, 1), oracle.unit(kd.double()).repeat_interleave(2, 1),
                              vd.double(), gd.double(), bd.double())
     close(got, want, 1e-5)
+    # the delta rule's gates from a strided projection, one decay per head and one per key channel
+    proj, A_log = rnd(T, 40), rnd(Hd) * 0.5
+    for C in (Hd, Hd * 3):
+        dtb = rnd(C)
+        ld_, bt_ = seqmix.decay_gates(d(proj)[:, 2:2 + C], d(proj)[:, 20:20 + Hd], d(A_log), d(dtb))
+        want_ld = -torch.exp(A_log.double()).repeat_interleave(C // Hd) * oracle.softplus(proj[:, 2:2 + C].double() + dtb.double())
+        close(ld_, want_ld, 1e-5), close(bt_, 1.0 / (1.0 + torch.exp(-proj[:, 20:20 + Hd].double())), 1e-5)
     # convolution with the input added, carried over two steps
     C, taps = 10, 3
     u, cw = rnd(T, C), rnd(C, taps)
