@@ -201,6 +201,19 @@ def test_ops_match_the_oracle_functions(device):
                                 vs[sl].double(), decay.double())
         close(got[sl], want, 1e-5)
     assert float(state[2].abs().max()) == 0.0                       # a row no sequence of the step owns stays untouched
+    # wide keys and sequences longer than a staging round (the prompt instances of the kernel), fed in two steps
+    for dk, dvv, nrot in ((64, 40, 32), (128, 24, 8), (72, 130, 0)):
+        n, cut = 45, 20
+        qw, kw, vw = rnd(n, 2, dk), rnd(n, 2, dk), rnd(n, 2, dvv)
+        dec = torch.tensor([0.9, 0.99])
+        inv = seqmix.rotary_frequencies(2 * nrot, 1000.0)
+        st = torch.zeros(1, 2, dk, dvv, device=device)
+        got = torch.cat([seqmix.retention_scan(d(qw[lo:hi]), d(kw[lo:hi]), d(vw[lo:hi]), d(dec), seqmix.PackedBatch([0, hi - lo], [0], device), st,
+                                               d(torch.arange(lo, hi)), None if inv is None else d(inv), dk ** -0.5) for lo, hi in ((0, cut), (cut, n))])
+        p = list(range(n))
+        want = oracle.retention(oracle.rotate_half(qw.double(), p, 2 * nrot, 1000.0), oracle.rotate_half(kw.double(), p, 2 * nrot, 1000.0) * dk ** -0.5,
+                                vw.double(), dec.double())
+        close(got, want, 1e-5)
     # delta rule with one decay per head, grouped q / k heads
     Hd, Gd = 4, 2
     qd, kd, vd = rnd(T, Gd, dd), rnd(T, Gd, dd), rnd(T, Hd, dv)
